@@ -1,0 +1,367 @@
+#!/usr/bin/env python3
+"""Benchmark of the Converse2D forward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--dtype fp32|bf16]
+
+Workload (N=1 and per GPU at N>1): BASELINE.json configs[1] -- one Converse2D
+upsampling layer, C=64, k=5, scale 2, circular padding 2, input 16x64x64x64
+-> output 16x64x128x128, seeded N(0,1) input, softmax-normalised taps, zero bias.
+A step is one forward over that batch.  Prints ONE JSON line on rank 0.
+
+`value` times the C-ABI call with inputs resident in HBM (CUDA events on the
+launch stream, graph-replayed so that launch latency is not the number);
+`e2e` times the module API from pinned host buffers with both copies inside
+the timed region.  `--impl reference` times the reference's own CPU operator
+(oracle/_ref, built from the reference's C++ source) or, if that is absent,
+the numpy oracle, on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=16, C=64, H=64, W=64, k=5, s=2, p=2, mode="circular", eps=1e-5)
+WORKLOAD = "converse2d_fwd cfg2: B16 C64 64x64 -> 128x128, k5 s2 p2 circular"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(cfg, esize):
+    n_in = cfg["B"] * cfg["C"] * cfg["H"] * cfg["W"]
+    return n_in * esize + n_in * cfg["s"] ** 2 * esize
+
+
+def out_pixels(cfg):
+    return cfg["B"] * cfg["C"] * cfg["H"] * cfg["W"] * cfg["s"] ** 2
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def seeded_case(cfg, seed=0):
+    import numpy as np
+    from oracle import converse2d_oracle as orc
+    rng = np.random.default_rng(seed)
+    w, b = orc.init_weight(cfg["C"], cfg["k"], rng)
+    x = rng.standard_normal((cfg["B"], cfg["C"], cfg["H"], cfg["W"])).astype(np.float32)
+    return x, w, b
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ reference arm (CPU)
+def reference_forward_fn(cfg):
+    """The reference's CPU path for this layer: its own C++ op when oracle/_ref is
+    present, else the numpy oracle.  Returns (callable, kind, threads)."""
+    import numpy as np
+    import torch
+    x, w, b = seeded_case(cfg)
+    so = os.path.join(ROOT, "oracle", "_ref", "converse2d_ref.so")
+    if os.path.exists(so):
+        import torch.nn.functional as F
+        torch.ops.load_library(so)
+        threads = os.cpu_count() or 1
+        torch.set_num_threads(threads)
+        wt, bt = torch.from_numpy(w), torch.from_numpy(b)
+        p, s, mode, eps = cfg["p"], cfg["s"], cfg["mode"], cfg["eps"]
+
+        def run(xt):
+            # module-side glue of models/util_converse.py:144-145,166,189-190 around the reference op
+            y = F.pad(xt, [p, p, p, p], mode=mode) if p > 0 else xt
+            x0 = y if s == 1 else F.interpolate(y, scale_factor=s, mode="nearest")
+            out = torch.ops.converse2d.forward(y, x0, wt, bt, s, eps)
+            return out[..., p * s:-p * s, p * s:-p * s] if p > 0 else out
+
+        return (lambda xs: run(xs)), "reference", threads, torch.from_numpy(x)
+    from oracle import converse2d_oracle as orc
+    fn = lambda xs: orc.converse2d_forward(xs, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], np.float32)
+    return fn, "port", 1, x
+
+
+def time_cpu(cfg, budget_s, steps=None, warmup=1):
+    """Time the CPU path on a bounded sample: the full batch if it fits the budget,
+    otherwise the leading samples of the batch.  Returns (Mpix/s, info)."""
+    fn, kind, threads, x = reference_forward_fn(cfg)
+    B = x.shape[0]
+    t0 = time.perf_counter()
+    fn(x[:1])
+    t1 = time.perf_counter() - t0
+    n_steps = steps if steps is not None else 5
+    per_step_budget = budget_s / max(1, n_steps + warmup)
+    bs = int(max(1, min(B, per_step_budget / max(t1, 1e-6))))
+    xs = x[:bs]
+    for _ in range(warmup):
+        fn(xs)
+    ts = []
+    for _ in range(n_steps):
+        t0 = time.perf_counter()
+        fn(xs)
+        ts.append(time.perf_counter() - t0)
+    t = statistics.mean(ts)
+    pix = bs * cfg["C"] * cfg["H"] * cfg["W"] * cfg["s"] ** 2
+    info = {"kind": kind, "cores": threads, "sample": "first %d of %d batch entries, %d timed steps, mean"
+            % (bs, B, n_steps), "ms_per_step": t * 1e3}
+    return pix / t / 1e6, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, info = time_cpu(CFG, budget_s=150.0, steps=args.steps, warmup=max(1, min(args.warmup, 3)))
+    line = {
+        "impl": "reference", "metric": "converse2d_fwd_throughput", "value": val, "unit": "Mpix/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "pixels": "B*C*sH*sW output plane-pixels"},
+        "cpu_baseline": {"value": val, "unit": "Mpix/s", "cores": info["cores"], "kind": info["kind"],
+                         "sample": info["sample"]},
+        "e2e": {"value": val, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ our arm (GPU)
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from conversenet_b200 import Converse2D, _cabi
+    from conversenet_b200 import functional as CF
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU path exists for the product)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _cabi.load()
+
+    cfg = CFG
+    tdtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    esize = 4 if args.dtype == "fp32" else 2
+    x_np, w_np, b_np = seeded_case(cfg)
+    mod = Converse2D(cfg["C"], cfg["C"], cfg["k"], scale=cfg["s"], padding=cfg["p"],
+                     padding_mode=cfg["mode"], eps=cfg["eps"]).to(dev).eval()
+    with torch.no_grad():
+        mod.weight.copy_(torch.from_numpy(w_np))
+        mod.bias.copy_(torch.from_numpy(b_np))
+
+    # rotating buffer sets so that no step finds its data in L2
+    step_bytes = algorithmic_bytes(cfg, esize)
+    nbuf = max(2, -(-2 * L2_BYTES // step_bytes) + 1)
+    x_host = torch.from_numpy(x_np).to(tdtype)
+    xs = [x_host.to(dev) if i == 0 else (x_host.to(dev) * (1.0 + 0.001 * i)).to(tdtype) for i in range(nbuf)]
+    outs = [torch.empty((cfg["B"], cfg["C"], cfg["H"] * cfg["s"], cfg["W"] * cfg["s"]), dtype=tdtype, device=dev)
+            for _ in range(nbuf)]
+    h, w = cfg["H"] + 2 * cfg["p"], cfg["W"] + 2 * cfg["p"]
+    table, wf = mod._table_for(h, w, dev)
+
+    def step(i):
+        CF.converse2d_forward(xs[i % nbuf], table, wf, cfg["k"], cfg["s"], cfg["p"], cfg["mode"],
+                              out=outs[i % nbuf])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K, W = args.steps, args.warmup
+    for i in range(max(W, 3)):
+        step(i)
+    torch.cuda.synchronize()
+
+    # capture `nbuf` consecutive steps in a CUDA graph; replay covers K steps exactly
+    stream = torch.cuda.Stream()
+    graph_ok = not args.no_graph
+    g = None
+    if graph_ok:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(nbuf):
+                        step(i)
+        except Exception as e:  # fall back to eager launches, still on-device timing
+            g = None
+            graph_ok = False
+            sys.stderr.write("graph capture failed (%s); timing eager launches\n" % e)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        done = 0
+        if g is not None:
+            while done + nbuf <= K:
+                g.replay()
+                done += nbuf
+        while done < K:
+            step(done)
+            done += 1
+        ev1.record(stream)
+    stream.synchronize()
+    barrier()
+    # keep the GPU busy a little longer so that the 100 ms clock sampler sees load
+    t_end = time.time() + 0.6
+    with torch.cuda.stream(stream):
+        while time.time() < t_end:
+            if g is not None:
+                g.replay()
+            else:
+                step(0)
+            stream.synchronize()
+    clocks = sampler.stop()
+    ms_total = ev0.elapsed_time(ev1)
+    t_max = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
+    ms_step = float(t_max.item()) / K
+    value = world * out_pixels(cfg) / (ms_step * 1e-3) / 1e6
+
+    # end to end through the module API from pinned host memory
+    xh = x_host.pin_memory()
+    oh = torch.empty(outs[0].shape, dtype=tdtype).pin_memory()
+    Ke = max(3, min(K, 20))
+
+    def e2e_step():
+        xd = xh.to(dev, non_blocking=True)
+        with torch.no_grad():
+            y = mod(xd)
+        oh.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(Ke):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_val = world * out_pixels(cfg) / (float(te.item()) / Ke * 1e-3) / 1e6
+
+    peak, peak_kind = measured_peak_gbs()
+    achieved = step_bytes / (ms_total / K * 1e-3) / 1e9  # this rank's kernel, one launch per step
+    line = {
+        "metric": "converse2d_fwd_throughput", "value": value, "unit": "Mpix/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32" if args.dtype == "fp32" else "bf16-io/f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "pixels": "B*C*sH*sW output plane-pixels",
+                   "mpix_per_s_reference_definition": value / cfg["C"],
+                   "l2": "%d rotating buffer sets (%.0f MB) > L2" % (nbuf, nbuf * step_bytes / 1e6),
+                   "launch": "cuda graph replay" if g is not None else "eager", "io_dtype": args.dtype,
+                   "sharding": "each rank runs the full batch on its own planes; no collective"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_val, "unit": "Mpix/s",
+                "h2d_bytes_per_step": x_host.numel() * esize, "d2h_bytes_per_step": oh.numel() * esize,
+                "steps": Ke},
+        "gpu_launches": K,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": read_traffic(), "peak_source": peak_kind,
+                     "algorithmic_bytes_per_launch": step_bytes},
+    }
+    if rank == 0 and world == 1:
+        try:
+            v, info = time_cpu(cfg, budget_s=20.0)
+            line["cpu_baseline"] = {"value": v, "unit": "Mpix/s", "cores": info["cores"], "kind": info["kind"],
+                                    "sample": info["sample"]}
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "Mpix/s", "cores": 0, "kind": "port",
+                                    "sample": "failed: %s" % e}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def read_traffic():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return json.load(f).get("converse2d_fwd_cfg2_dram_bytes_per_launch")
+    except Exception:
+        return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

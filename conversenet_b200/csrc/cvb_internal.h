@@ -1,0 +1,31 @@
+// Internal glue between the translation units of libconverse_b200.so.
+#pragma once
+#include "cvb_kernels.cuh"
+
+namespace cvb {
+
+// Records a failing CUDA runtime call for cvb_last_cuda_error and returns CVB_ERR_CUDA.
+int cuda_fail(cudaError_t e);
+
+#define CVB_CUDA(call)                                   \
+  do {                                                   \
+    cudaError_t e__ = (call);                            \
+    if (e__ != cudaSuccess) return ::cvb::cuda_fail(e__); \
+  } while (0)
+
+int env_int(const char* name, int dflt);
+
+// Number of (channel, batch-pair) work items = blocks of the shared-memory kernels.
+inline int num_pairs(const FwdParams& P) { return P.C * ((P.B + 1) / 2); }
+
+// Runtime-plan kernel (k_dynamic.cu).
+int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
+
+// Compile-time-plan kernels (k_static.cu, one object per registry line).
+typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
+struct StaticEntry {
+  int ry0, ry1, rx0, rx1;
+  StaticLauncher fn;
+};
+
+}  // namespace cvb

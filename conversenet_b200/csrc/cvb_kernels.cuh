@@ -1,0 +1,658 @@
+// Per-thread building blocks of the Converse2D forward kernels.
+//
+// Everything here is written as `__host__ __device__` functions of an explicit
+// (tid, nthr) pair, and each kernel body is a sequence of CVB_PHASE(...) steps
+// separated by block barriers.  Compiled for the device a phase runs once per
+// thread followed by __syncthreads(); compiled for the host (test builds only)
+// a phase is a loop over tid, so the index arithmetic of a whole block can be
+// checked on a machine without a GPU.
+//
+// Math.  For one plane y = pad(x) of size h x w (models/util_converse.py:144-145)
+// the reference's solve (:171-187) is linear in y and collapses to
+//     s == 1 :  out = crop( IFFT2( G . FFT2(y) ) ),  G = (conj(FK)+lam) / (|FK|^2+lam)
+//     s >= 2 :  r   = IFFT2( P . FFT2(y) ),          P = (1 - fold_s(FK.D)) / (fold_s(|FK|^2)+lam)
+//               out = crop( nearest_s(y) + corr(K, zero_insert_s(r)) )
+// with FK the kernel spectrum on the s*h x s*w grid (:218-235), D the spectrum of
+// the s x s box that turns zero-insertion into nearest-upsampling, fold_s the
+// mean over the s*s aliases (:182-183) and lam = sigmoid(bias-9)+eps (:147).
+// Both FFTs are h x w whatever the scale.  Two planes that share a kernel (same
+// channel, two batch entries) travel as the real and imaginary part of one
+// complex plane: G and P are spectra of real filters, so the two never mix.
+//
+// FFT.  In-place mixed radix, decimation in frequency forward (natural order in,
+// digit-reversed out) and decimation in time inverse (digit-reversed in, natural
+// out); the transfer table is stored in digit-reversed order so nothing is ever
+// permuted.  A stage with sub-length L, radix R, M = L/R handles butterfly
+// t -> (blk = t / M, j = t % M) on elements blk*L + j + q*M.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <math.h>
+#include <stdint.h>
+
+#define CVB_HD __host__ __device__ __forceinline__
+#include "fft_codelets.cuh"
+
+namespace cvb {
+
+constexpr int kMaxStages = 8;
+constexpr int kMaxTaps = 15;  // largest kernel_size the epilogue keeps in shared memory
+
+struct Plan1D {
+  int n;
+  int nst;
+  int radix[kMaxStages];
+  int L[kMaxStages];  // sub-transform length entering stage i
+  int M[kMaxStages];  // L / radix
+};
+
+struct FwdParams {
+  const void* x;
+  void* out;
+  const float2* table;  // [C][w][h] multiplier (transposed, digit-reversed), then twiddles
+  const float* weight;  // (C,k,k), read when s > 1
+  int B, C, H, W, k, s, p, pad_mode, fuse_gelu;
+  int h, w, pitch;
+  Plan1D py, px;
+};
+
+enum { MODE_FWD = 0, MODE_INV = 1, MODE_LOAD = 2, MODE_MID = 3, MODE_STORE = 4 };
+
+struct PassArgs {
+  float2* sm;
+  int es, ls, nlines;  // element stride, line stride (float2 units), number of lines
+  int N, L, M, tws;    // transform length, stage sub-length, L/R, twiddle stride N/L
+  const float2* tw;    // tw[n] = (cos, sin)(2 pi n / N)
+  float inv_nlines, invM;
+};
+
+struct IoArgs {
+  const void* xa;
+  const void* xb;  // second plane of the pair, may be null
+  void* oa;
+  void* ob;
+  int H, W, p, pad_mode, gelu, h, w;
+  const float2* tab;  // this channel's multiplier
+};
+
+// ---------------------------------------------------------------- helpers
+template <typename IO> CVB_HD float ld_io(const void* p, size_t i);
+template <> CVB_HD float ld_io<float>(const void* p, size_t i) { return ((const float*)p)[i]; }
+template <> CVB_HD float ld_io<__nv_bfloat16>(const void* p, size_t i) {
+  return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+template <typename IO> CVB_HD void st_io(void* p, size_t i, float v);
+template <> CVB_HD void st_io<float>(void* p, size_t i, float v) { ((float*)p)[i] = v; }
+template <> CVB_HD void st_io<__nv_bfloat16>(void* p, size_t i, float v) {
+  ((__nv_bfloat16*)p)[i] = __float2bfloat16(v);
+}
+
+CVB_HD float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
+
+// Index into the unpadded axis of length n for padded coordinate i (already
+// shifted by -p), or -1 where constant padding supplies a zero.
+CVB_HD int pad_index(int i, int n, int mode) {
+  if (i >= 0 && i < n) return i;
+  switch (mode) {
+    case 0: return i < 0 ? i + n : i - n;           // circular
+    case 1: return i < 0 ? 0 : n - 1;               // replicate
+    case 2: return i < 0 ? -i : 2 * n - 2 - i;      // reflect
+    default: return -1;                             // constant
+  }
+}
+
+// wi -> (wi / d, wi % d) for small non-negative wi without an integer divide
+CVB_HD void divmod_small(int wi, int d, float inv_d, int& q, int& r) {
+  q = (int)((float)wi * inv_d);
+  r = wi - q * d;
+  if (r < 0) { r += d; --q; } else if (r >= d) { r -= d; ++q; }
+}
+
+// Position in the digit-reversed array -> frequency index.
+CVB_HD int pos_to_freq(const Plan1D& pl, int pos) {
+  int k = 0, mult = 1;
+  for (int i = 0; i < pl.nst; ++i) {
+    const int d = (pos / pl.M[i]) % pl.radix[i];
+    k += d * mult;
+    mult *= pl.radix[i];
+  }
+  return k;
+}
+
+// ---------------------------------------------------------------- one FFT stage
+template <int R, int MODE, typename IO>
+CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io) {
+  const int nbf = a.N / R;
+  const int total = nbf * a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int t, line, blk, j;
+    divmod_small(wi, a.nlines, a.inv_nlines, t, line);
+    divmod_small(t, a.M, a.invM, blk, j);
+    const int base = blk * a.L + j;
+    float re[R], im[R];
+
+    if constexpr (MODE == MODE_LOAD) {
+      // first column stage: rows base + q*M of padded column `line`, straight from x
+      const int cx = pad_index(line - io.p, io.W, io.pad_mode);
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        const int ry = pad_index(base + q * a.M - io.p, io.H, io.pad_mode);
+        float va = 0.f, vb = 0.f;
+        if (cx >= 0 && ry >= 0) {
+          const size_t off = (size_t)ry * io.W + cx;
+          va = ld_io<IO>(io.xa, off);
+          if (io.xb) vb = ld_io<IO>(io.xb, off);
+        }
+        re[q] = va;
+        im[q] = vb;
+      }
+    } else {
+      const float2* ptr = a.sm + line * a.ls + base * a.es;
+      const int st = a.M * a.es;
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        const float2 v = ptr[q * st];
+        re[q] = v.x;
+        im[q] = v.y;
+      }
+    }
+
+    if constexpr (MODE == MODE_INV || MODE == MODE_STORE) {
+      if (a.M > 1) {
+        const int tstep = j * a.tws;
+#pragma unroll
+        for (int p = 1; p < R; ++p) {
+          const float2 wv = a.tw[tstep * p];
+          const float xr = re[p], xi = im[p];
+          re[p] = fmaf(-xi, wv.y, xr * wv.x);
+          im[p] = fmaf(xr, wv.y, xi * wv.x);
+        }
+      }
+      Radix<R>::fwd(im, re);
+    } else {
+      Radix<R>::fwd(re, im);
+      if constexpr (MODE != MODE_MID) {
+        if (a.M > 1) {
+          const int tstep = j * a.tws;
+#pragma unroll
+          for (int p = 1; p < R; ++p) {
+            const float2 wv = a.tw[tstep * p];
+            const float xr = re[p], xi = im[p];
+            re[p] = fmaf(xi, wv.y, xr * wv.x);
+            im[p] = fmaf(-xr, wv.y, xi * wv.x);
+          }
+        }
+      }
+    }
+
+    if constexpr (MODE == MODE_MID) {
+      // last row stage: multiply by the transfer table, then undo the stage
+      const float2* tp = io.tab + (size_t)(t * R) * io.h + line;
+#pragma unroll
+      for (int p = 0; p < R; ++p) {
+        const float2 g = tp[(size_t)p * io.h];
+        const float xr = re[p], xi = im[p];
+        re[p] = fmaf(-xi, g.y, xr * g.x);
+        im[p] = fmaf(xr, g.y, xi * g.x);
+      }
+      Radix<R>::fwd(im, re);
+    }
+
+    if constexpr (MODE == MODE_STORE) {
+      // last inverse column stage at scale 1: crop and write both planes
+      const int ox = line - io.p;
+      if (ox >= 0 && ox < io.W) {
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+          const int oy = base + q * a.M - io.p;
+          if (oy >= 0 && oy < io.H) {
+            const size_t off = (size_t)oy * io.W + ox;
+            float va = re[q], vb = im[q];
+            if (io.gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
+            st_io<IO>(io.oa, off, va);
+            if (io.ob) st_io<IO>(io.ob, off, vb);
+          }
+        }
+      }
+    } else {
+      float2* ptr = a.sm + line * a.ls + base * a.es;
+      const int st = a.M * a.es;
+#pragma unroll
+      for (int q = 0; q < R; ++q) ptr[q * st] = make_float2(re[q], im[q]);
+    }
+  }
+}
+
+template <int MODE>
+CVB_HD void run_pass(int R, int tid, int nthr, const PassArgs& a, const IoArgs& io) {
+  switch (R) {
+#define CVB_X(RR) \
+  case RR: fft_pass<RR, MODE, float>(tid, nthr, a, io); break;
+    CVB_FOR_EACH_RADIX(CVB_X)
+#undef CVB_X
+    default: break;
+  }
+}
+
+CVB_HD PassArgs make_pass(float2* sm, bool along_y, int pitch, int h, int w, int N, int L, int M,
+                          const float2* tw) {
+  PassArgs a;
+  a.sm = sm;
+  a.es = along_y ? pitch : 1;
+  a.ls = along_y ? 1 : pitch;
+  a.nlines = along_y ? w : h;
+  a.N = N;
+  a.L = L;
+  a.M = M;
+  a.tws = N / L;
+  a.tw = tw;
+  a.inv_nlines = 1.0f / (float)a.nlines;
+  a.invM = 1.0f / (float)M;
+  return a;
+}
+
+// ---------------------------------------------------------------- s >= 2 epilogue
+// out[i][j] = y[i/s][j/s] + sum_{a,b} K[a][b] * Z[i+a-c][j+b-c],  Z = zero-insert of r,
+// c = k/2, on the s*h x s*w circular grid, cropped to [p*s, s*h - p*s).  `sm` holds r
+// for both planes (x: plane a, y: plane b).  One thread per low-resolution cell.
+CVB_HD int floordiv(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
+
+template <typename IO>
+CVB_HD void epilogue_generic(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
+                             const IoArgs& io) {
+  const int s = P.s, k = P.k, c = P.k / 2, p = P.p, h = P.h, w = P.w;
+  const int cells = P.H * P.W;
+  const int oW = P.W * s;
+  const float invW = 1.0f / (float)P.W;
+  for (int ci = tid; ci < cells; ci += nthr) {
+    int my, mx;
+    divmod_small(ci, P.W, invW, my, mx);
+    const size_t xoff = (size_t)my * P.W + mx;
+    const float ya = ld_io<IO>(io.xa, xoff);
+    const float yb = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
+    const int m = my + p, n = mx + p;
+    for (int da = 0; da < s; ++da) {
+      for (int db = 0; db < s; ++db) {
+        float acca = ya, accb = yb;
+        for (int a = 0; a < k; ++a) {
+          const int ii = da + a - c;
+          if (ii - floordiv(ii, s) * s != 0) continue;
+          int rm = m + floordiv(ii, s);
+          rm %= h; if (rm < 0) rm += h;
+          for (int b = 0; b < k; ++b) {
+            const int jj = db + b - c;
+            if (jj - floordiv(jj, s) * s != 0) continue;
+            int rn = n + floordiv(jj, s);
+            rn %= w; if (rn < 0) rn += w;
+            const float2 rv = sm[rm * P.pitch + rn];
+            const float kv = wk[a * k + b];
+            acca = fmaf(kv, rv.x, acca);
+            accb = fmaf(kv, rv.y, accb);
+          }
+        }
+        if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+        const size_t off = (size_t)(my * s + da) * oW + (size_t)(mx * s + db);
+        st_io<IO>(io.oa, off, acca);
+        if (io.ob) st_io<IO>(io.ob, off, accb);
+      }
+    }
+  }
+}
+
+// Compile-time (S, K): the taps each output phase touches are resolved by the
+// compiler; the r window (WIN x WIN cells) is loaded once per cell.
+template <int S, int K, typename IO>
+CVB_HD void epilogue_static(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
+                            const IoArgs& io) {
+  constexpr int c = K / 2;
+  constexpr int DMIN = (0 - c >= 0) ? (0 - c) / S : -((c + S - 1) / S);
+  constexpr int DMAX = (S - 1 + K - 1 - c) / S;
+  constexpr int WIN = DMAX - DMIN + 1;
+  const int p = P.p, h = P.h, w = P.w;
+  const int cells = P.H * P.W;
+  const int oW = P.W * S;
+  const float invW = 1.0f / (float)P.W;
+  float kw[K * K];
+#pragma unroll
+  for (int i = 0; i < K * K; ++i) kw[i] = wk[i];
+  for (int ci = tid; ci < cells; ci += nthr) {
+    int my, mx;
+    divmod_small(ci, P.W, invW, my, mx);
+    const size_t xoff = (size_t)my * P.W + mx;
+    const float ya = ld_io<IO>(io.xa, xoff);
+    const float yb = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
+    float2 win[WIN][WIN];
+    int cols[WIN];
+#pragma unroll
+    for (int e = 0; e < WIN; ++e) {
+      int rn = mx + p + DMIN + e;
+      rn %= w; if (rn < 0) rn += w;
+      cols[e] = rn;
+    }
+#pragma unroll
+    for (int d = 0; d < WIN; ++d) {
+      int rm = my + p + DMIN + d;
+      rm %= h; if (rm < 0) rm += h;
+#pragma unroll
+      for (int e = 0; e < WIN; ++e) win[d][e] = sm[rm * P.pitch + cols[e]];
+    }
+#pragma unroll
+    for (int da = 0; da < S; ++da) {
+      float oa[S], ob[S];
+#pragma unroll
+      for (int db = 0; db < S; ++db) {
+        float acca = ya, accb = yb;
+#pragma unroll
+        for (int a = 0; a < K; ++a) {
+          const int ii = da + a - c;
+          const int fi = (ii >= 0) ? ii / S : -((-ii + S - 1) / S);
+          if (ii - fi * S != 0) continue;
+#pragma unroll
+          for (int b = 0; b < K; ++b) {
+            const int jj = db + b - c;
+            const int fj = (jj >= 0) ? jj / S : -((-jj + S - 1) / S);
+            if (jj - fj * S != 0) continue;
+            const float2 rv = win[fi - DMIN][fj - DMIN];
+            acca = fmaf(kw[a * K + b], rv.x, acca);
+            accb = fmaf(kw[a * K + b], rv.y, accb);
+          }
+        }
+        if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+        oa[db] = acca;
+        ob[db] = accb;
+      }
+      const size_t off = (size_t)(my * S + da) * oW + (size_t)(mx * S);
+#pragma unroll
+      for (int db = 0; db < S; ++db) {
+        st_io<IO>(io.oa, off + db, oa[db]);
+        if (io.ob) st_io<IO>(io.ob, off + db, ob[db]);
+      }
+    }
+  }
+}
+
+template <typename IO>
+CVB_HD void run_epilogue(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
+                         const IoArgs& io) {
+  const int key = P.s * 100 + P.k;
+  switch (key) {
+    case 202: epilogue_static<2, 2, IO>(tid, nthr, sm, wk, P, io); break;
+    case 203: epilogue_static<2, 3, IO>(tid, nthr, sm, wk, P, io); break;
+    case 205: epilogue_static<2, 5, IO>(tid, nthr, sm, wk, P, io); break;
+    case 303: epilogue_static<3, 3, IO>(tid, nthr, sm, wk, P, io); break;
+    case 305: epilogue_static<3, 5, IO>(tid, nthr, sm, wk, P, io); break;
+    case 407: epilogue_static<4, 7, IO>(tid, nthr, sm, wk, P, io); break;
+    default: epilogue_generic<IO>(tid, nthr, sm, wk, P, io); break;
+  }
+}
+
+// ---------------------------------------------------------------- block bodies
+#ifdef __CUDA_ARCH__
+#define CVB_PHASE(call)                                  \
+  do {                                                   \
+    const int tid = threadIdx.x, nthr = blockDim.x;      \
+    (void)tid; (void)nthr;                               \
+    call;                                                \
+    __syncthreads();                                     \
+  } while (0)
+#else
+#define CVB_PHASE(call)                                  \
+  do {                                                   \
+    for (int tid = 0; tid < nthr_emu; ++tid) {           \
+      const int nthr = nthr_emu;                         \
+      (void)nthr;                                        \
+      call;                                              \
+    }                                                    \
+  } while (0)
+#endif
+
+// Shared-memory layout of one block (float2 units unless noted).
+struct SmemLayout {
+  int plane;   // h * pitch
+  int twy;     // h
+  int twx;     // w
+  int wk;      // k*k floats, rounded up to float2
+  __host__ __device__ size_t bytes() const { return (size_t)(plane + twy + twx + wk) * sizeof(float2); }
+};
+CVB_HD SmemLayout smem_layout(int h, int w, int pitch, int k) {
+  SmemLayout l;
+  l.plane = h * pitch;
+  l.twy = h;
+  l.twx = w;
+  l.wk = (k * k + 1) / 2;
+  return l;
+}
+
+CVB_HD void load_tables(int tid, int nthr, const FwdParams& P, int c, float2* twy, float2* twx, float* wk) {
+  const float2* gtw = P.table + (size_t)P.C * P.h * P.w;
+  for (int i = tid; i < P.h; i += nthr) twy[i] = gtw[i];
+  for (int i = tid; i < P.w; i += nthr) twx[i] = gtw[P.h + i];
+  if (P.s > 1)
+    for (int i = tid; i < P.k * P.k; i += nthr) wk[i] = P.weight[(size_t)c * P.k * P.k + i];
+}
+
+// pair index -> channel and the two planes
+CVB_HD void pair_planes(const FwdParams& P, int pair, int& c, int& pa, int& pb) {
+  c = pair % P.C;
+  const int i = pair / P.C;
+  pa = (2 * i) * P.C + c;
+  pb = (2 * i + 1 < P.B) ? (2 * i + 1) * P.C + c : -1;
+}
+
+template <typename IO>
+CVB_HD IoArgs make_io(const FwdParams& P, int c, int pa, int pb) {
+  IoArgs io;
+  const size_t in_plane = (size_t)P.H * P.W, out_plane = in_plane * P.s * P.s;
+  io.xa = (const IO*)P.x + (size_t)pa * in_plane;
+  io.xb = pb >= 0 ? (const void*)((const IO*)P.x + (size_t)pb * in_plane) : nullptr;
+  io.oa = (IO*)P.out + (size_t)pa * out_plane;
+  io.ob = pb >= 0 ? (void*)((IO*)P.out + (size_t)pb * out_plane) : nullptr;
+  io.H = P.H; io.W = P.W; io.p = P.p; io.pad_mode = P.pad_mode; io.gelu = P.fuse_gelu;
+  io.h = P.h; io.w = P.w;
+  io.tab = P.table + (size_t)c * P.h * P.w;
+  return io;
+}
+
+// Plain phases used by the runtime-plan kernel: padded load, table multiply, cropped store.
+template <typename IO>
+CVB_HD void phase_load_plane(int tid, int nthr, float2* plane, const FwdParams& P, const IoArgs& io) {
+  const int total = P.h * P.w;
+  const float invw = 1.0f / (float)P.w;
+  for (int i = tid; i < total; i += nthr) {
+    int row, col;
+    divmod_small(i, P.w, invw, row, col);
+    const int ry = pad_index(row - P.p, P.H, P.pad_mode);
+    const int cx = pad_index(col - P.p, P.W, P.pad_mode);
+    float va = 0.f, vb = 0.f;
+    if (ry >= 0 && cx >= 0) {
+      const size_t off = (size_t)ry * P.W + cx;
+      va = ld_io<IO>(io.xa, off);
+      if (io.xb) vb = ld_io<IO>(io.xb, off);
+    }
+    plane[row * P.pitch + col] = make_float2(va, vb);
+  }
+}
+
+CVB_HD void phase_multiply(int tid, int nthr, float2* plane, const FwdParams& P, const IoArgs& io) {
+  const int total = P.h * P.w;
+  const float invh = 1.0f / (float)P.h;
+  for (int i = tid; i < total; i += nthr) {
+    int posx, posy;
+    divmod_small(i, P.h, invh, posx, posy);  // posy fastest: the table's order
+    const float2 g = io.tab[i];
+    float2* e = plane + posy * P.pitch + posx;
+    const float2 v = *e;
+    *e = make_float2(fmaf(-v.y, g.y, v.x * g.x), fmaf(v.x, g.y, v.y * g.x));
+  }
+}
+
+template <typename IO>
+CVB_HD void phase_store_plane(int tid, int nthr, const float2* plane, const FwdParams& P, const IoArgs& io) {
+  const int total = P.H * P.W;
+  const float invW = 1.0f / (float)P.W;
+  for (int i = tid; i < total; i += nthr) {
+    int oy, ox;
+    divmod_small(i, P.W, invW, oy, ox);
+    const float2 v = plane[(oy + P.p) * P.pitch + ox + P.p];
+    float va = v.x, vb = v.y;
+    if (io.gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
+    st_io<IO>(io.oa, (size_t)i, va);
+    if (io.ob) st_io<IO>(io.ob, (size_t)i, vb);
+  }
+}
+
+// Runtime plan: any supported factorisation, radices picked by a switch; the
+// load, multiply and store are separate sweeps (the compile-time kernels fuse them).
+template <typename IO>
+__host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2* smem, int nthr_emu) {
+  (void)nthr_emu;
+  const SmemLayout lay = smem_layout(P.h, P.w, P.pitch, P.k);
+  float2* plane = smem;
+  float2* twy = plane + lay.plane;
+  float2* twx = twy + lay.twy;
+  float* wk = (float*)(twx + lay.twx);
+  int c, pa, pb;
+  pair_planes(P, pair, c, pa, pb);
+  const IoArgs io = make_io<IO>(P, c, pa, pb);
+  const Plan1D& py = P.py;
+  const Plan1D& px = P.px;
+
+  CVB_PHASE((load_tables(tid, nthr, P, c, twy, twx, wk), phase_load_plane<IO>(tid, nthr, plane, P, io)));
+  for (int i = 0; i < py.nst; ++i)
+    CVB_PHASE((run_pass<MODE_FWD>(py.radix[i], tid, nthr,
+                                  make_pass(plane, true, P.pitch, P.h, P.w, py.n, py.L[i], py.M[i], twy), io)));
+  for (int i = 0; i < px.nst; ++i)
+    CVB_PHASE((run_pass<MODE_FWD>(px.radix[i], tid, nthr,
+                                  make_pass(plane, false, P.pitch, P.h, P.w, px.n, px.L[i], px.M[i], twx), io)));
+  CVB_PHASE(phase_multiply(tid, nthr, plane, P, io));
+  for (int i = px.nst - 1; i >= 0; --i)
+    CVB_PHASE((run_pass<MODE_INV>(px.radix[i], tid, nthr,
+                                  make_pass(plane, false, P.pitch, P.h, P.w, px.n, px.L[i], px.M[i], twx), io)));
+  for (int i = py.nst - 1; i >= 0; --i)
+    CVB_PHASE((run_pass<MODE_INV>(py.radix[i], tid, nthr,
+                                  make_pass(plane, true, P.pitch, P.h, P.w, py.n, py.L[i], py.M[i], twy), io)));
+  if (P.s == 1) {
+    CVB_PHASE(phase_store_plane<IO>(tid, nthr, plane, P, io));
+  } else {
+    CVB_PHASE(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
+  }
+}
+
+// Compile-time plan: h = RY0*RY1, w = RX0*RX1, two stages per axis, all index
+// arithmetic folded by the compiler and only the four needed butterflies in the
+// kernel's register budget.
+template <typename IO, int RY0, int RY1, int RX0, int RX1>
+__host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2* smem, int nthr_emu) {
+  (void)nthr_emu;
+  constexpr int h = RY0 * RY1, w = RX0 * RX1;
+  constexpr int pitch = w | 1;
+  const SmemLayout lay = smem_layout(h, w, pitch, P.k);
+  float2* plane = smem;
+  float2* twy = plane + lay.plane;
+  float2* twx = twy + lay.twy;
+  float* wk = (float*)(twx + lay.twx);
+  int c, pa, pb;
+  pair_planes(P, pair, c, pa, pb);
+  IoArgs io = make_io<IO>(P, c, pa, pb);
+  io.h = h; io.w = w;
+
+  CVB_PHASE(load_tables(tid, nthr, P, c, twy, twx, wk));
+  CVB_PHASE((fft_pass<RY0, MODE_LOAD, IO>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
+  CVB_PHASE((fft_pass<RY1, MODE_FWD, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, RY1, 1, twy), io)));
+  CVB_PHASE((fft_pass<RX0, MODE_FWD, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, w, RX1, twx), io)));
+  CVB_PHASE((fft_pass<RX1, MODE_MID, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, RX1, 1, twx), io)));
+  CVB_PHASE((fft_pass<RX0, MODE_INV, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, w, RX1, twx), io)));
+  CVB_PHASE((fft_pass<RY1, MODE_INV, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, RY1, 1, twy), io)));
+  if (P.s == 1) {
+    CVB_PHASE((fft_pass<RY0, MODE_STORE, IO>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
+  } else {
+    CVB_PHASE((fft_pass<RY0, MODE_INV, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
+    CVB_PHASE(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
+  }
+}
+
+// ---------------------------------------------------------------- transfer table
+struct TransferParams {
+  const float* weight;  // (C,k,k)
+  const float* bias;    // (C)
+  float2* table;
+  int C, k, s, h, w;
+  float eps;
+  Plan1D py, px;
+};
+
+// One table entry: position (posx, posy) of channel c.  fp64 throughout.
+__host__ __device__ inline void transfer_entry(const TransferParams& T, int c, int posy, int posx) {
+  const int s = T.s, k = T.k, h = T.h, w = T.w, cc = T.k / 2;
+  const int u = pos_to_freq(T.py, posy), v = pos_to_freq(T.px, posx);
+  const double lam = 1.0 / (1.0 + exp(-((double)T.bias[c] - 9.0))) + (double)T.eps;
+  const int Nh = s * h, Nw = s * w;
+  const float* K = T.weight + (size_t)c * k * k;
+  double num_r = 0.0, num_i = 0.0, den = 0.0;  // sums over the s*s aliases
+  for (int ia = 0; ia < s; ++ia) {
+    const int U = u + ia * h;
+    // D_h(U) = sum_{a<s} exp(-2 pi i a U / Nh)
+    double dhr = 0.0, dhi = 0.0;
+    for (int a = 0; a < s; ++a) {
+      const long long m = ((long long)a * U) % Nh;
+      dhr += cos(-2.0 * M_PI * (double)m / Nh);
+      dhi += sin(-2.0 * M_PI * (double)m / Nh);
+    }
+    for (int ib = 0; ib < s; ++ib) {
+      const int V = v + ib * w;
+      double dwr = 0.0, dwi = 0.0;
+      for (int b = 0; b < s; ++b) {
+        const long long m = ((long long)b * V) % Nw;
+        dwr += cos(-2.0 * M_PI * (double)m / Nw);
+        dwi += sin(-2.0 * M_PI * (double)m / Nw);
+      }
+      // FK[U,V] = sum_{a,b} K[a][b] exp(-2 pi i ((a-c) U / Nh + (b-c) V / Nw))
+      double fr = 0.0, fi = 0.0;
+      for (int a = 0; a < k; ++a) {
+        long long ma = ((long long)(a - cc) * U) % Nh; if (ma < 0) ma += Nh;
+        const double ear = cos(-2.0 * M_PI * (double)ma / Nh), eai = sin(-2.0 * M_PI * (double)ma / Nh);
+        double rr = 0.0, ri = 0.0;
+        for (int b = 0; b < k; ++b) {
+          long long mb = ((long long)(b - cc) * V) % Nw; if (mb < 0) mb += Nw;
+          const double kv = (double)K[a * k + b];
+          rr += kv * cos(-2.0 * M_PI * (double)mb / Nw);
+          ri += kv * sin(-2.0 * M_PI * (double)mb / Nw);
+        }
+        fr += ear * rr - eai * ri;
+        fi += ear * ri + eai * rr;
+      }
+      den += fr * fr + fi * fi;
+      if (s == 1) {
+        num_r = fr; num_i = -fi;  // conj(FK)
+      } else {
+        const double dr = dhr * dwr - dhi * dwi, di = dhr * dwi + dhi * dwr;
+        num_r += fr * dr - fi * di;
+        num_i += fr * di + fi * dr;
+      }
+    }
+  }
+  const double inv_alias = 1.0 / (double)(s * s);
+  const double norm = 1.0 / ((double)h * (double)w);
+  double tr, ti;
+  if (s == 1) {
+    const double d = den + lam;
+    tr = (num_r + lam) / d;
+    ti = num_i / d;
+  } else {
+    const double d = den * inv_alias + lam;
+    tr = (1.0 - num_r * inv_alias) / d;
+    ti = (-num_i * inv_alias) / d;
+  }
+  T.table[((size_t)c * w + posx) * h + posy] = make_float2((float)(tr * norm), (float)(ti * norm));
+}
+
+__host__ __device__ inline void twiddle_entry(const TransferParams& T, int i) {
+  // tw[n] = (cos, sin)(2 pi n / N); first h entries for the column length, then w
+  float2* tw = T.table + (size_t)T.C * T.h * T.w;
+  const int N = i < T.h ? T.h : T.w;
+  const int n = i < T.h ? i : i - T.h;
+  const double th = 2.0 * M_PI * (double)n / (double)N;
+  tw[i] = make_float2((float)cos(th), (float)sin(th));
+}
+
+}  // namespace cvb

@@ -1,0 +1,75 @@
+"""Tensor-level entry points over the C ABI (device memory and streams come from torch)."""
+import torch
+
+from . import _cabi
+
+
+def _stream_ptr(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _io_dtype(t):
+    if t.dtype == torch.float32:
+        return _cabi.CVB_F32
+    if t.dtype == torch.bfloat16:
+        return _cabi.CVB_BF16
+    raise RuntimeError("Converse2D supports float32 and bfloat16 tensors, got %s" % t.dtype)
+
+
+def build_transfer(weight, bias, scale, eps, h, w):
+    """Transfer table for `weight` (1,C,k,k) / `bias` (1,C,1,1) at padded size h x w.
+
+    Plays the role of the reference's cached kernel spectrum
+    (`converse2d.cpp:58-102`), but holds the complete weights-only multiplier.
+    Returns a uint8 CUDA tensor owned by the caller."""
+    lib = _cabi.load()
+    if not weight.is_cuda:
+        raise RuntimeError("Converse2D parameters must live on a CUDA device")
+    if weight.dim() != 4 or weight.size(0) != 1:
+        raise RuntimeError("weight must be (1,C,kh,kw)")
+    C, k = weight.size(1), weight.size(2)
+    if weight.size(3) != k:
+        raise RuntimeError("only square kernels are supported")
+    if bias.dim() != 4 or bias.size(0) != 1 or bias.size(1) != C or bias.size(2) != 1 or bias.size(3) != 1:
+        raise RuntimeError("bias must be (1,C,1,1)")
+    if scale < 1:
+        raise RuntimeError("scale must be >= 1")
+    nbytes = lib.cvb_transfer_bytes(C, h, w)
+    if nbytes == 0:
+        raise RuntimeError("padded plane %dx%d is not supported by the FFT engine" % (h, w))
+    wf = weight.detach().reshape(C, k, k).to(torch.float32).contiguous()
+    bf = bias.detach().reshape(C).to(torch.float32).contiguous()
+    table = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        rc = lib.cvb_build_transfer(wf.data_ptr(), bf.data_ptr(), C, k, int(scale), h, w, float(eps),
+                                    table.data_ptr(), _stream_ptr(weight.device))
+    _cabi.check(rc, "cvb_build_transfer")
+    return table, wf
+
+
+def converse2d_forward(x, table, weight_f32, kernel_size, scale, padding, padding_mode, fuse_gelu=False,
+                       out=None):
+    """Fused pad -> solve -> crop (`models/util_converse.py:142-192`) on a CUDA tensor."""
+    lib = _cabi.load()
+    if not x.is_cuda:
+        raise RuntimeError("Converse2D needs a CUDA tensor; this build has no CPU path")
+    if x.dim() != 4:
+        raise RuntimeError("x must be (B,C,H,W)")
+    if padding_mode not in _cabi.PAD_MODES:
+        raise RuntimeError("unknown padding_mode %r" % (padding_mode,))
+    x = x.contiguous()
+    B, C, H, W = x.shape
+    io = _io_dtype(x)
+    s = int(scale)
+    if out is None:
+        out = torch.empty((B, C, H * s, W * s), dtype=x.dtype, device=x.device)
+    ws_bytes = lib.cvb_converse2d_workspace_bytes(B, C, H, W, s, int(padding), io)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
+    with torch.cuda.device(x.device):
+        rc = lib.cvb_converse2d_fwd(x.data_ptr(), out.data_ptr(), table.data_ptr(), weight_f32.data_ptr(),
+                                    B, C, H, W, int(kernel_size), s, int(padding),
+                                    _cabi.PAD_MODES[padding_mode], io, 1 if fuse_gelu else 0,
+                                    ws.data_ptr() if ws is not None else None, ws_bytes,
+                                    _stream_ptr(x.device))
+    _cabi.check(rc, "cvb_converse2d_fwd")
+    return out

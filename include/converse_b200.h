@@ -1,0 +1,111 @@
+/*
+ * converse_b200 -- C ABI of the B200 (sm_100a) Converse2D library.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (0 = success, negative = error, see cvb_strerror), never throws, never exits
+ * and never traps the device.  Device pointers are owned by the caller; work is
+ * enqueued on the stream passed in (a cudaStream_t passed as void*).
+ *
+ * The functions replace, for the Converse2D forward path, what the reference
+ * binds through its extension:
+ *   - torch.ops.converse2d.forward   (Converse2D/torch_converse2d/converse2d.cpp:165-209,218-227)
+ *   - torch.ops.converse2d.clear_cache (converse2d.cpp:211-216): the kernel-spectrum
+ *     cache becomes an explicit, caller-owned "transfer table" (cvb_build_transfer).
+ *   - the module-side pad / nearest-upsample / crop around the op
+ *     (models/util_converse.py:144-145,166,189-190), which are fused into the kernel.
+ */
+#ifndef CONVERSE_B200_H_
+#define CONVERSE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  CVB_OK = 0,
+  CVB_ERR_BAD_ARGUMENT = -1,     /* null pointer, non-positive size, bad enum */
+  CVB_ERR_BAD_PADDING = -2,      /* circular needs p <= H,W; reflect needs p < H,W */
+  CVB_ERR_UNSUPPORTED_SIZE = -3, /* padded length has a prime factor the FFT engine lacks */
+  CVB_ERR_WORKSPACE = -4,        /* workspace missing or too small */
+  CVB_ERR_CUDA = -5,             /* a CUDA runtime call failed; see cvb_last_cuda_error */
+  CVB_ERR_KERNEL_TOO_LARGE = -6, /* k larger than the padded, upsampled plane */
+  CVB_ERR_TOO_LARGE = -7         /* size beyond a stated fixed maximum */
+};
+
+/* boundary modes of F.pad (models/util_converse.py:144-145) */
+enum { CVB_PAD_CIRCULAR = 0, CVB_PAD_REPLICATE = 1, CVB_PAD_REFLECT = 2, CVB_PAD_CONSTANT = 3 };
+
+/* element type of x and out; spectra and arithmetic are always fp32 */
+enum { CVB_F32 = 0, CVB_BF16 = 1 };
+
+/* Library / ABI version (major*100 + minor). */
+int cvb_version(void);
+
+/* Human-readable text for a status code. */
+const char* cvb_strerror(int status);
+
+/* The cudaError_t (as int) of the last failing runtime call on this thread, 0 if none. */
+int cvb_last_cuda_error(void);
+
+/*
+ * Size in bytes of the transfer table for C channels (or B*C planes when the
+ * kernels differ per sample) at padded size h x w = (H+2p) x (W+2p).
+ * Replaces the FB/FBC/F2B triple the reference caches per weight tensor
+ * (converse2d.cpp:22-102).  Returns 0 on bad arguments or an unsupported size.
+ */
+size_t cvb_transfer_bytes(int C, int h, int w);
+
+/*
+ * Build the transfer table: psf2otf of the k x k taps (models/util_converse.py:218-235),
+ * lambda = sigmoid(bias-9)+eps (:147), and the whole spectral algebra of :176-186
+ * collapsed to one weights-only multiplier per frequency, evaluated in fp64 and
+ * stored as fp32 in the layout the forward kernel reads.
+ *   weight : device, (C, k, k) fp32      bias : device, (C) fp32
+ *   h, w   : padded plane size           s    : scale
+ *   table  : device, cvb_transfer_bytes(C, h, w) bytes, 16-byte aligned
+ */
+int cvb_build_transfer(const float* weight, const float* bias, int C, int k, int s, int h, int w,
+                       float eps, void* table, void* stream);
+
+/*
+ * Bytes of scratch the forward needs for this shape (0 when the plane fits in
+ * shared memory and everything stays on chip).
+ */
+size_t cvb_converse2d_workspace_bytes(int B, int C, int H, int W, int s, int p, int io_dtype);
+
+/*
+ * Converse2D forward: out = crop(solve(pad(x))), the full body of
+ * Converse2D.forward (models/util_converse.py:142-192) for x0 = nearest-upsample
+ * of the padded input, which is what the module always passes (:166,172-173).
+ *   x      : device, (B, C, H, W) contiguous, io_dtype
+ *   out    : device, (B, C, s*H, s*W) contiguous, io_dtype
+ *   table  : from cvb_build_transfer for (C, k, s, H+2p, W+2p)
+ *   weight : device, (C, k, k) fp32 (read only when s > 1)
+ *   fuse_gelu : 1 applies the exact (erf) GELU to the result before the store
+ *               (the activation that follows the operator in ConverseBlock,
+ *               models/util_converse.py:282)
+ *   workspace / workspace_bytes : >= cvb_converse2d_workspace_bytes(...), may be
+ *               NULL / 0 when that is 0
+ */
+int cvb_converse2d_fwd(const void* x, void* out, const void* table, const float* weight, int B,
+                       int C, int H, int W, int k, int s, int p, int pad_mode, int io_dtype,
+                       int fuse_gelu, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Describe the FFT plan chosen for a padded length n: writes up to max_stages
+ * radices, returns the stage count, 0 if n is unsupported.  Host-only, no GPU.
+ */
+int cvb_plan_radices(int n, int* radices, int max_stages);
+
+/* 1 if the forward for this padded size runs in the single-kernel shared-memory
+ * path, 0 if it takes the multi-pass path through the workspace, negative on error. */
+int cvb_fits_shared(int h, int w);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CONVERSE_B200_H_ */

@@ -1,0 +1,148 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle and the reference's golden outputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import converse2d_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-4   # relative L2, fp32 (the bar BASELINE.json's north_star states)
+TOL_BF16 = 5e-3   # relative L2, bf16 I/O with fp32 spectra
+
+
+def _module(C, k, s, p, mode, eps, w, b):
+    from conversenet_b200 import Converse2D
+    m = Converse2D(C, C, k, scale=s, padding=p, padding_mode=mode, eps=eps).cuda().eval()
+    with torch.no_grad():
+        m.weight.copy_(torch.from_numpy(w))
+        m.bias.copy_(torch.from_numpy(b))
+    return m
+
+
+def _run(x, w, b, s, p, mode, eps, dtype=torch.float32):
+    m = _module(x.shape[1], w.shape[-1], s, p, mode, eps, w, b)
+    with torch.no_grad():
+        y = m(torch.from_numpy(x).cuda().to(dtype))
+    torch.cuda.synchronize()
+    return y.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("i", range(20))
+def test_golden_cases(golden, i):
+    c, x, w, b, ref32, ref64 = golden.case(i)
+    out = _run(x, w, b, c["s"], c["p"], c["mode"], c["eps"])
+    assert out.shape == ref32.shape
+    assert orc.rel_l2(out, ref32) <= TOL_FP32
+    assert orc.rel_l2(out, ref64) <= TOL_FP32
+
+
+@pytest.mark.parametrize("i", [1, 4, 13, 15])
+def test_golden_cases_forced_runtime_plan(golden, i, monkeypatch):
+    monkeypatch.setenv("CVB_FORCE_DYNAMIC", "1")
+    c, x, w, b, ref32, ref64 = golden.case(i)
+    out = _run(x, w, b, c["s"], c["p"], c["mode"], c["eps"])
+    assert orc.rel_l2(out, ref64) <= TOL_FP32
+
+
+CONFIGS = {
+    # BASELINE.json configs[0] and configs[1] (full size), SRResNet-style layers reduced in batch
+    "cfg1": dict(B=1, C=64, H=128, W=128, k=5, s=1, p=2, mode="circular", eps=1e-5),
+    "cfg2": dict(B=16, C=64, H=64, W=64, k=5, s=2, p=2, mode="circular", eps=1e-5),
+    "srres_body": dict(B=2, C=128, H=128, W=128, k=5, s=1, p=4, mode="replicate", eps=1e-5),
+    "srres_up1": dict(B=2, C=64, H=128, W=128, k=2, s=2, p=2, mode="replicate", eps=1e-3),
+    "odd_batch": dict(B=3, C=8, H=64, W=64, k=5, s=2, p=2, mode="circular", eps=1e-5),
+}
+
+
+def _seeded(cfg, seed=0):
+    rng = np.random.default_rng(seed)
+    w, b = orc.init_weight(cfg["C"], cfg["k"], rng)
+    x = rng.standard_normal((cfg["B"], cfg["C"], cfg["H"], cfg["W"])).astype(np.float32)
+    return x, w, b
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_baseline_configs_fp32(name):
+    cfg = CONFIGS[name]
+    x, w, b = _seeded(cfg)
+    out = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    ref32 = orc.converse2d_forward(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float32)
+    ref64 = orc.converse2d_forward(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float64)
+    assert orc.rel_l2(out, ref32) <= TOL_FP32
+    assert orc.rel_l2(out, ref64) <= TOL_FP32
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg1"])
+def test_baseline_configs_bf16_io(name):
+    cfg = CONFIGS[name]
+    x, w, b = _seeded(cfg)
+    xb = torch.from_numpy(x).bfloat16()
+    out = _run(xb.float().numpy(), w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
+    ref = orc.converse2d_forward(xb.float().numpy(), w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"],
+                                 dtype=np.float32)
+    ref = torch.from_numpy(ref).bfloat16().float().numpy()
+    assert orc.rel_l2(out, ref) <= TOL_BF16
+
+
+def test_forced_runtime_plan_matches_compiled_plan(monkeypatch):
+    cfg = CONFIGS["odd_batch"]
+    x, w, b = _seeded(cfg, 5)
+    a = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    monkeypatch.setenv("CVB_FORCE_DYNAMIC", "1")
+    d = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    assert orc.rel_l2(a, d) <= 2e-6
+
+
+def test_linearity_and_constant_planes_full_size():
+    # size-independent properties at the bench workload's full size
+    cfg = CONFIGS["cfg2"]
+    x, w, b = _seeded(cfg, 11)
+    x2 = np.random.default_rng(12).standard_normal(x.shape).astype(np.float32)
+    m = _module(cfg["C"], cfg["k"], cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], w, b)
+    with torch.no_grad():
+        a = m(torch.from_numpy(x).cuda())
+        c = m(torch.from_numpy(x2).cuda())
+        ac = m(torch.from_numpy(x + 0.5 * x2).cuda())
+        const = m(torch.full(x.shape, 3.25, device="cuda"))
+    assert float((ac - (a + 0.5 * c)).norm() / ac.norm()) <= 2e-6
+    # a constant plane is a fixed point of the circular solve (the kernel taps sum to one)
+    assert float((const - 3.25).abs().max()) <= 2e-4
+
+
+def test_fused_gelu_matches_separate_gelu():
+    cfg = CONFIGS["odd_batch"]
+    x, w, b = _seeded(cfg, 2)
+    for s in (1, 2):
+        m = _module(cfg["C"], cfg["k"], s, cfg["p"], cfg["mode"], cfg["eps"], w, b)
+        xt = torch.from_numpy(x).cuda()
+        with torch.no_grad():
+            plain = m(xt)
+            m.fuse_gelu = True
+            fused = m(xt)
+        assert torch.allclose(fused, torch.nn.functional.gelu(plain), atol=1e-6, rtol=1e-5)
+
+
+def test_table_follows_in_place_weight_update():
+    cfg = CONFIGS["odd_batch"]
+    x, w, b = _seeded(cfg, 3)
+    m = _module(cfg["C"], cfg["k"], 1, cfg["p"], cfg["mode"], cfg["eps"], w, b)
+    xt = torch.from_numpy(x).cuda()
+    with torch.no_grad():
+        m(xt)
+        m.bias.add_(9.0)  # lambda changes from ~1.3e-4 to ~0.5
+        out = m(xt).cpu().numpy()
+    ref = orc.converse2d_forward(x, w, b + 9.0, 1, cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float64)
+    assert orc.rel_l2(out, ref) <= TOL_FP32
+
+
+def test_error_behaviour_on_device():
+    from conversenet_b200 import Converse2D
+    m = Converse2D(2, 2, 3, padding=9, padding_mode="circular").cuda()
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(1, 2, 8, 8, device="cuda"))      # padding wider than the plane
+    m = Converse2D(2, 2, 3, padding=1).cuda()
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float16))  # unsupported dtype
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(1, 3, 8, 8, device="cuda"))      # channel mismatch

@@ -1,0 +1,81 @@
+"""Host emulation of the CUDA block bodies against the oracle and the golden vectors.
+
+The kernels' per-thread phase functions are compiled for the host (tests/emu) and
+run thread by thread.  This checks index arithmetic and the transfer-table
+algebra without a GPU; it is not a product path and the package cannot load it.
+"""
+import ctypes
+import numpy as np
+import pytest
+
+from oracle import converse2d_oracle as orc
+from tests.emu.build_emu import build_emu
+
+PAD = {"circular": 0, "replicate": 1, "reflect": 2, "constant": 3}
+
+
+@pytest.fixture(scope="module")
+def emu():
+    lib = ctypes.CDLL(build_emu())
+    lib.emu_build_transfer.restype = ctypes.c_int
+    lib.emu_converse2d_fwd.restype = ctypes.c_int
+    return lib
+
+
+def _ptr(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0):
+    B, C, H, W = x.shape
+    k = w.shape[-1]
+    h, wd = H + 2 * p, W + 2 * p
+    table = np.zeros((C * h * wd + h + wd, 2), np.float32)
+    wf = np.ascontiguousarray(w.reshape(C, k, k), np.float32)
+    bf = np.ascontiguousarray(b.reshape(C), np.float32)
+    rc = lib.emu_build_transfer(_ptr(wf), _ptr(bf), C, k, s, h, wd, ctypes.c_float(eps), _ptr(table))
+    assert rc == 0
+    xf = np.ascontiguousarray(x, np.float32)
+    out = np.full((B, C, H * s, W * s), np.nan, np.float32)
+    rc = lib.emu_converse2d_fwd(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
+                                PAD[mode], gelu, nthr, variant)
+    assert rc == 0, rc
+    return out
+
+
+@pytest.mark.parametrize("i", range(20))
+def test_emu_matches_reference_golden(emu, golden, i):
+    c, x, w, b, ref32, ref64 = golden.case(i)
+    out = emu_forward(emu, x, w, b, c["s"], c["p"], c["mode"], c["eps"], nthr=64 + 32 * (i % 3))
+    assert np.isfinite(out).all()
+    assert orc.rel_l2(out, ref64) <= 2e-5
+    assert orc.rel_l2(out, ref32) <= 1e-4
+
+
+@pytest.mark.parametrize("shape,k,s,p,mode", [
+    ((2, 2, 64, 64), 5, 2, 2, "circular"),    # cfg-2 plane: compile-time plan 68 = 17*4
+    ((3, 1, 64, 64), 5, 1, 2, "replicate"),   # odd batch: last pair has one plane
+    ((1, 2, 30, 38), 5, 1, 2, "reflect"),     # 34 x 42 = (17*2) x (7*6)
+    ((2, 1, 32, 40), 3, 3, 2, "constant"),    # 36 x 44 = (6*6) x (11*4)
+])
+def test_emu_static_plan_body(emu, shape, k, s, p, mode):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal(shape).astype(np.float32)
+    w, b = orc.init_weight(shape[1], k, rng)
+    b = (9.0 + rng.standard_normal(b.shape)).astype(np.float32)
+    ref = orc.converse2d_forward(x, w, b, s, p, mode, 1e-5, dtype=np.float64)
+    for variant in (0, 1):
+        out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=160, variant=variant)
+        assert orc.rel_l2(out, ref) <= 2e-5, variant
+
+
+def test_emu_gelu_epilogue(emu):
+    from math import erf
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 2, 16, 18)).astype(np.float32)
+    w, b = orc.init_weight(2, 3, rng)
+    for s in (1, 2):
+        ref = orc.converse2d_forward(x, w, b, s, 1, "circular", 1e-5, dtype=np.float64)
+        ref = 0.5 * ref * (1.0 + np.vectorize(erf)(ref / np.sqrt(2.0)))
+        out = emu_forward(emu, x, w, b, s, 1, "circular", 1e-5, gelu=1)
+        assert orc.rel_l2(out, ref) <= 2e-5
