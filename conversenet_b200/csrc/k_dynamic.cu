@@ -11,8 +11,9 @@ __global__ void __launch_bounds__(512, 1) smem_dynamic_kernel(const FwdParams P)
   smem_block_dynamic<IO>(P, blockIdx.x, smem, 0);
 }
 
+namespace {
 template <typename IO>
-static int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
+int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
   CVB_CUDA(cudaFuncSetAttribute(smem_dynamic_kernel<IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int nthr = env_int("CVB_THREADS", 0);
   if (nthr <= 0) {
@@ -28,6 +29,7 @@ static int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
+}  // namespace
 
 int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st) {
   return io_dtype == CVB_F32 ? launch_t<float>(P, smem, st) : launch_t<__nv_bfloat16>(P, smem, st);

@@ -9,21 +9,26 @@
 
 namespace cvb {
 
-template <typename IO>
+// The radices are template parameters so that every registry line gets its own
+// kernel symbol: this file is compiled several times into one library.
+template <typename IO, int RY0, int RY1, int RX0, int RX1>
 __global__ void __launch_bounds__(CVB_NT, CVB_MB) smem_static_kernel(const FwdParams P) {
   extern __shared__ float2 smem[];
-  smem_block_static<IO, CVB_RY0, CVB_RY1, CVB_RX0, CVB_RX1>(P, blockIdx.x, smem, 0);
+  smem_block_static<IO, RY0, RY1, RX0, RX1>(P, blockIdx.x, smem, 0);
 }
 
+namespace {
 template <typename IO>
-static int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
-  CVB_CUDA(cudaFuncSetAttribute(smem_static_kernel<IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
+  auto kernel = smem_static_kernel<IO, CVB_RY0, CVB_RY1, CVB_RX0, CVB_RX1>;
+  CVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int nthr = env_int("CVB_THREADS", CVB_NT);
   if (nthr < 32 || nthr > CVB_NT) nthr = CVB_NT;
-  smem_static_kernel<IO><<<num_pairs(P), nthr, smem, st>>>(P);
+  kernel<<<num_pairs(P), nthr, smem, st>>>(P);
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
+}  // namespace
 
 int CVB_CAT(CVB_RY0, CVB_RY1, CVB_RX0, CVB_RX1)(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st) {
   return io_dtype == CVB_F32 ? launch_t<float>(P, smem, st) : launch_t<__nv_bfloat16>(P, smem, st);
