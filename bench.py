@@ -278,6 +278,11 @@ def run_ours(args):
     ms_step = float(t_max.item()) / K
     value = world * out_pixels(cfg) / (ms_step * 1e-3) / 1e6
 
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": "converse2d_fwd_throughput", "value": value, "unit": "Mpix/s",
+                              "ms_per_step": ms_step, "kernel_only": True, "clocks": clocks}))
+        return
     # end to end through the module API from pinned host memory
     xh = x_host.pin_memory()
     oh = torch.empty(outs[0].shape, dtype=tdtype).pin_memory()
@@ -356,6 +361,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

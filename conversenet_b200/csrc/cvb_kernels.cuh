@@ -53,10 +53,9 @@ struct FwdParams {
   const float* weight;  // (C,k,k), read when s > 1
   int B, C, H, W, k, s, p, pad_mode, fuse_gelu;
   int h, w, pitch;
+  int skip_mask;  // tuning aid: bit i set = phase i is not executed (results are then wrong)
   Plan1D py, px;
 };
-
-enum { MODE_FWD = 0, MODE_INV = 1, MODE_LOAD = 2, MODE_MID = 3, MODE_STORE = 4 };
 
 struct PassArgs {
   float2* sm;
@@ -73,13 +72,25 @@ struct IoArgs {
   void* ob;
   int H, W, p, pad_mode, gelu, h, w;
   const float2* tab;  // this channel's multiplier
+  const int* rmap;    // padded row -> source row * W, or -1 (zero)
+  const int* cmap;    // padded column -> source column, or -1 (zero)
 };
 
 // ---------------------------------------------------------------- helpers
 template <typename IO> CVB_HD float ld_io(const void* p, size_t i);
-template <> CVB_HD float ld_io<float>(const void* p, size_t i) { return ((const float*)p)[i]; }
+template <> CVB_HD float ld_io<float>(const void* p, size_t i) {
+#ifdef __CUDA_ARCH__
+  return __ldg((const float*)p + i);
+#else
+  return ((const float*)p)[i];
+#endif
+}
 template <> CVB_HD float ld_io<__nv_bfloat16>(const void* p, size_t i) {
+#ifdef __CUDA_ARCH__
+  return __bfloat162float(__ldg((const __nv_bfloat16*)p + i));
+#else
   return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+#endif
 }
 template <typename IO> CVB_HD void st_io(void* p, size_t i, float v);
 template <> CVB_HD void st_io<float>(void* p, size_t i, float v) { ((float*)p)[i] = v; }
@@ -120,26 +131,60 @@ CVB_HD int pos_to_freq(const Plan1D& pl, int pos) {
 }
 
 // ---------------------------------------------------------------- one FFT stage
-template <int R, int MODE, typename IO>
-CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io) {
-  const int nbf = a.N / R;
-  const int total = nbf * a.nlines;
+// One routine serves every stage of a kernel, selected by run-time flags, so that
+// each butterfly is present once in the instruction stream (the kernels are
+// instruction-cache bound otherwise).  All butterflies use the forward kernel:
+//   forward stage (decimation in frequency): butterfly, then twiddle;
+//   inverse stage (decimation in time)     : twiddle, then butterfly, applied to
+//     the conjugated spectrum -- IDFT(W) = conj(DFT(conj(W))).  The conjugation
+//     happens once in the PASS_MID stage and once at the final store (PASS_CONJ_OUT).
+enum {
+  PASS_PRE = 1,         // twiddle before the butterfly (inverse-type stage)
+  PASS_SRC_GLOBAL = 2,  // first column stage: read x through the pad maps
+  PASS_DST_GLOBAL = 4,  // last column stage at scale 1: crop and write out
+  PASS_MID = 8,         // last row stage: butterfly, transfer multiply, conjugate, butterfly
+  PASS_CONJ_OUT = 16    // negate the imaginary part on the way out
+};
+
+// CN, CL, CM, CNL: compile-time transform length, stage sub-length, L/R and line
+// count (0 = take the run-time value from PassArgs); strides stay run-time so that
+// the row and the column stage of a square plane share one instantiation.
+template <int R, typename IO, int CN = 0, int CL = 0, int CM = 0, int CNL = 0, int CFLAGS = -1>
+CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int rt_flags) {
+  const int flags = CFLAGS >= 0 ? CFLAGS : rt_flags;  // compile-time flags when given
+  const int aN = CN ? CN : a.N, aL = CL ? CL : a.L, aM = CM ? CM : a.M, anl = CNL ? CNL : a.nlines;
+  const int atws = CN ? CN / (CL ? CL : 1) : a.tws;
+  const int nbf = aN / R;
+  const int total = nbf * anl;
+  const int nrep = (flags & PASS_MID) ? 2 : 1;
+  const float osign = (flags & PASS_CONJ_OUT) ? -1.0f : 1.0f;
+  const bool twiddle = aM > 1;
   for (int wi = tid; wi < total; wi += nthr) {
     int t, line, blk, j;
-    divmod_small(wi, a.nlines, a.inv_nlines, t, line);
-    divmod_small(t, a.M, a.invM, blk, j);
-    const int base = blk * a.L + j;
+    if constexpr (CNL != 0) {
+      t = wi / CNL;
+      line = wi - t * CNL;
+      blk = t / CM;
+      j = t - blk * CM;
+    } else {
+      divmod_small(wi, a.nlines, a.inv_nlines, t, line);
+      divmod_small(t, a.M, a.invM, blk, j);
+    }
+    const int base = blk * aL + j;
+    float2* ptr = a.sm + line * a.ls + base * a.es;
+    const int st = aM * a.es;
+    const int tstep = j * atws;
     float re[R], im[R];
 
-    if constexpr (MODE == MODE_LOAD) {
-      // first column stage: rows base + q*M of padded column `line`, straight from x
-      const int cx = pad_index(line - io.p, io.W, io.pad_mode);
+    if (flags & PASS_SRC_GLOBAL) {
+      // rows base + q*M of padded column `line`, straight from x
+      const int cx = io.cmap[line];
 #pragma unroll
       for (int q = 0; q < R; ++q) {
-        const int ry = pad_index(base + q * a.M - io.p, io.H, io.pad_mode);
+        const int ro = io.rmap[base + q * aM];
         float va = 0.f, vb = 0.f;
-        if (cx >= 0 && ry >= 0) {
-          const size_t off = (size_t)ry * io.W + cx;
+        if ((cx | ro) >= 0) {
+          const size_t off = (size_t)(ro + cx);
           va = ld_io<IO>(io.xa, off);
           if (io.xb) vb = ld_io<IO>(io.xb, off);
         }
@@ -147,8 +192,6 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io) {
         im[q] = vb;
       }
     } else {
-      const float2* ptr = a.sm + line * a.ls + base * a.es;
-      const int st = a.M * a.es;
 #pragma unroll
       for (int q = 0; q < R; ++q) {
         const float2 v = ptr[q * st];
@@ -157,57 +200,52 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io) {
       }
     }
 
-    if constexpr (MODE == MODE_INV || MODE == MODE_STORE) {
-      if (a.M > 1) {
-        const int tstep = j * a.tws;
+    if ((flags & PASS_PRE) && twiddle) {
 #pragma unroll
-        for (int p = 1; p < R; ++p) {
-          const float2 wv = a.tw[tstep * p];
-          const float xr = re[p], xi = im[p];
-          re[p] = fmaf(-xi, wv.y, xr * wv.x);
-          im[p] = fmaf(xr, wv.y, xi * wv.x);
-        }
-      }
-      Radix<R>::fwd(im, re);
-    } else {
-      Radix<R>::fwd(re, im);
-      if constexpr (MODE != MODE_MID) {
-        if (a.M > 1) {
-          const int tstep = j * a.tws;
-#pragma unroll
-          for (int p = 1; p < R; ++p) {
-            const float2 wv = a.tw[tstep * p];
-            const float xr = re[p], xi = im[p];
-            re[p] = fmaf(xi, wv.y, xr * wv.x);
-            im[p] = fmaf(-xr, wv.y, xi * wv.x);
-          }
-        }
-      }
-    }
-
-    if constexpr (MODE == MODE_MID) {
-      // last row stage: multiply by the transfer table, then undo the stage
-      const float2* tp = io.tab + (size_t)(t * R) * io.h + line;
-#pragma unroll
-      for (int p = 0; p < R; ++p) {
-        const float2 g = tp[(size_t)p * io.h];
+      for (int p = 1; p < R; ++p) {
+        const float2 wv = a.tw[tstep * p];
         const float xr = re[p], xi = im[p];
-        re[p] = fmaf(-xi, g.y, xr * g.x);
-        im[p] = fmaf(xr, g.y, xi * g.x);
+        re[p] = fmaf(xi, wv.y, xr * wv.x);
+        im[p] = fmaf(-xr, wv.y, xi * wv.x);
       }
-      Radix<R>::fwd(im, re);
     }
 
-    if constexpr (MODE == MODE_STORE) {
-      // last inverse column stage at scale 1: crop and write both planes
+#pragma unroll 1
+    for (int rep = 0; rep < nrep; ++rep) {
+      Radix<R>::fwd(re, im);
+      if ((flags & PASS_MID) && rep == 0) {
+        // multiply by the transfer table and conjugate: the inverse runs on conj(spectrum)
+        const float2* tp = io.tab + (size_t)(t * R) * io.h + line;
+#pragma unroll
+        for (int p = 0; p < R; ++p) {
+          const float2 g = tp[(size_t)p * io.h];
+          const float xr = re[p], xi = im[p];
+          re[p] = fmaf(-xi, g.y, xr * g.x);
+          im[p] = -fmaf(xr, g.y, xi * g.x);
+        }
+      }
+    }
+
+    if (!(flags & (PASS_PRE | PASS_MID)) && twiddle) {
+#pragma unroll
+      for (int p = 1; p < R; ++p) {
+        const float2 wv = a.tw[tstep * p];
+        const float xr = re[p], xi = im[p];
+        re[p] = fmaf(xi, wv.y, xr * wv.x);
+        im[p] = fmaf(-xr, wv.y, xi * wv.x);
+      }
+    }
+
+    if (flags & PASS_DST_GLOBAL) {
+      // crop and write both planes (column `line`, rows base + q*M)
       const int ox = line - io.p;
       if (ox >= 0 && ox < io.W) {
 #pragma unroll
         for (int q = 0; q < R; ++q) {
-          const int oy = base + q * a.M - io.p;
+          const int oy = base + q * aM - io.p;
           if (oy >= 0 && oy < io.H) {
             const size_t off = (size_t)oy * io.W + ox;
-            float va = re[q], vb = im[q];
+            float va = re[q], vb = osign * im[q];
             if (io.gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
             st_io<IO>(io.oa, off, va);
             if (io.ob) st_io<IO>(io.ob, off, vb);
@@ -215,19 +253,17 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io) {
         }
       }
     } else {
-      float2* ptr = a.sm + line * a.ls + base * a.es;
-      const int st = a.M * a.es;
 #pragma unroll
-      for (int q = 0; q < R; ++q) ptr[q * st] = make_float2(re[q], im[q]);
+      for (int q = 0; q < R; ++q) ptr[q * st] = make_float2(re[q], osign * im[q]);
     }
   }
 }
 
-template <int MODE>
-CVB_HD void run_pass(int R, int tid, int nthr, const PassArgs& a, const IoArgs& io) {
+template <typename IO>
+CVB_HD void run_pass(int R, int tid, int nthr, const PassArgs& a, const IoArgs& io, int flags) {
   switch (R) {
 #define CVB_X(RR) \
-  case RR: fft_pass<RR, MODE, float>(tid, nthr, a, io); break;
+  case RR: fft_pass<RR, IO>(tid, nthr, a, io, flags); break;
     CVB_FOR_EACH_RADIX(CVB_X)
 #undef CVB_X
     default: break;
@@ -299,74 +335,142 @@ CVB_HD void epilogue_generic(int tid, int nthr, const float2* sm, const float* w
   }
 }
 
+// Store n consecutive outputs of one row; 16-byte vector stores when `vec`.
+template <typename IO, int N>
+CVB_HD void store_run(void* base, size_t off, const float (&v)[N], bool vec, int nvalid);
+template <int N>
+CVB_HD void store_run_f32(void* base, size_t off, const float (&v)[N], bool vec, int nvalid) {
+  float* o = (float*)base + off;
+  if constexpr (N % 4 == 0) {
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < N; i += 4) *(float4*)(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (i < nvalid) o[i] = v[i];
+}
+template <int N>
+CVB_HD void store_run_bf16(void* base, size_t off, const float (&v)[N], bool vec, int nvalid) {
+  __nv_bfloat16* o = (__nv_bfloat16*)base + off;
+  if constexpr (N % 8 == 0) {
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < N; i += 8) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+        uint4 u;
+        u.x = *(unsigned*)&h0; u.y = *(unsigned*)&h1; u.z = *(unsigned*)&h2; u.w = *(unsigned*)&h3;
+        *(uint4*)(o + i) = u;
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (i < nvalid) o[i] = __float2bfloat16(v[i]);
+}
+template <> CVB_HD void store_run<float, 4>(void* b, size_t o, const float (&v)[4], bool vec, int n) { store_run_f32<4>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<float, 6>(void* b, size_t o, const float (&v)[6], bool vec, int n) { store_run_f32<6>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<float, 8>(void* b, size_t o, const float (&v)[8], bool vec, int n) { store_run_f32<8>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<float, 12>(void* b, size_t o, const float (&v)[12], bool vec, int n) { store_run_f32<12>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<float, 16>(void* b, size_t o, const float (&v)[16], bool vec, int n) { store_run_f32<16>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<__nv_bfloat16, 4>(void* b, size_t o, const float (&v)[4], bool vec, int n) { store_run_bf16<4>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<__nv_bfloat16, 6>(void* b, size_t o, const float (&v)[6], bool vec, int n) { store_run_bf16<6>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<__nv_bfloat16, 8>(void* b, size_t o, const float (&v)[8], bool vec, int n) { store_run_bf16<8>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<__nv_bfloat16, 12>(void* b, size_t o, const float (&v)[12], bool vec, int n) { store_run_bf16<12>(b, o, v, vec, n); }
+template <> CVB_HD void store_run<__nv_bfloat16, 16>(void* b, size_t o, const float (&v)[16], bool vec, int n) { store_run_bf16<16>(b, o, v, vec, n); }
+
 // Compile-time (S, K): the taps each output phase touches are resolved by the
-// compiler; the r window (WIN x WIN cells) is loaded once per cell.
-template <int S, int K, typename IO>
+// compiler.  A thread owns a strip of CW low-resolution cells of one row: the r
+// window (WIN rows x CW+WIN-1 columns) is loaded once, each of the S output rows
+// leaves as one run of CW*S values.
+template <int S, int K, int CW, typename IO>
 CVB_HD void epilogue_static(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
                             const IoArgs& io) {
   constexpr int c = K / 2;
-  constexpr int DMIN = (0 - c >= 0) ? (0 - c) / S : -((c + S - 1) / S);
+  constexpr int DMIN = (c == 0) ? 0 : -((c + S - 1) / S);
   constexpr int DMAX = (S - 1 + K - 1 - c) / S;
   constexpr int WIN = DMAX - DMIN + 1;
+  constexpr int WC = CW + WIN - 1;
+  constexpr int NO = CW * S;
   const int p = P.p, h = P.h, w = P.w;
-  const int cells = P.H * P.W;
+  const int spr = (P.W + CW - 1) / CW;  // strips per row
+  const int nstrips = P.H * spr;
   const int oW = P.W * S;
-  const float invW = 1.0f / (float)P.W;
+  const float inv_spr = 1.0f / (float)spr;
+  constexpr int VEC = sizeof(IO) == 4 ? 4 : 8;  // elements per 16-byte store
+  const bool vec = (P.W % CW == 0) && (NO % VEC == 0) && (oW % VEC == 0) &&
+                   (((size_t)io.oa) % 16 == 0) && (((size_t)io.ob) % 16 == 0);
   float kw[K * K];
 #pragma unroll
   for (int i = 0; i < K * K; ++i) kw[i] = wk[i];
-  for (int ci = tid; ci < cells; ci += nthr) {
-    int my, mx;
-    divmod_small(ci, P.W, invW, my, mx);
-    const size_t xoff = (size_t)my * P.W + mx;
-    const float ya = ld_io<IO>(io.xa, xoff);
-    const float yb = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
-    float2 win[WIN][WIN];
-    int cols[WIN];
+  for (int si = tid; si < nstrips; si += nthr) {
+    int my, sx;
+    divmod_small(si, spr, inv_spr, my, sx);
+    const int mx0 = sx * CW;
+    const int ncell = (P.W - mx0) < CW ? (P.W - mx0) : CW;
+    float ya[CW], yb[CW];
 #pragma unroll
-    for (int e = 0; e < WIN; ++e) {
-      int rn = mx + p + DMIN + e;
-      rn %= w; if (rn < 0) rn += w;
+    for (int e = 0; e < CW; ++e) {
+      const size_t xoff = (size_t)my * P.W + (mx0 + (e < ncell ? e : 0));
+      ya[e] = ld_io<IO>(io.xa, xoff);
+      yb[e] = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
+    }
+    float2 win[WIN][WC];
+    int cols[WC];
+#pragma unroll
+    for (int e = 0; e < WC; ++e) {
+      int rn = mx0 + p + DMIN + e;
+      if (rn < 0) rn += w;
+      if (rn >= w) rn -= w;
+      if (rn >= w) rn -= w;
       cols[e] = rn;
     }
 #pragma unroll
     for (int d = 0; d < WIN; ++d) {
       int rm = my + p + DMIN + d;
-      rm %= h; if (rm < 0) rm += h;
+      if (rm < 0) rm += h;
+      if (rm >= h) rm -= h;
+      const float2* rowp = sm + rm * P.pitch;
 #pragma unroll
-      for (int e = 0; e < WIN; ++e) win[d][e] = sm[rm * P.pitch + cols[e]];
+      for (int e = 0; e < WC; ++e) win[d][e] = rowp[cols[e]];
     }
 #pragma unroll
     for (int da = 0; da < S; ++da) {
-      float oa[S], ob[S];
+      float oa[NO], ob[NO];
 #pragma unroll
-      for (int db = 0; db < S; ++db) {
-        float acca = ya, accb = yb;
+      for (int e = 0; e < CW; ++e) {
 #pragma unroll
-        for (int a = 0; a < K; ++a) {
-          const int ii = da + a - c;
-          const int fi = (ii >= 0) ? ii / S : -((-ii + S - 1) / S);
-          if (ii - fi * S != 0) continue;
+        for (int db = 0; db < S; ++db) {
+          float acca = ya[e], accb = yb[e];
 #pragma unroll
-          for (int b = 0; b < K; ++b) {
-            const int jj = db + b - c;
-            const int fj = (jj >= 0) ? jj / S : -((-jj + S - 1) / S);
-            if (jj - fj * S != 0) continue;
-            const float2 rv = win[fi - DMIN][fj - DMIN];
-            acca = fmaf(kw[a * K + b], rv.x, acca);
-            accb = fmaf(kw[a * K + b], rv.y, accb);
+          for (int a = 0; a < K; ++a) {
+            const int ii = da + a - c;
+            const int fi = (ii >= 0) ? ii / S : -((-ii + S - 1) / S);
+            if (ii - fi * S != 0) continue;
+#pragma unroll
+            for (int b = 0; b < K; ++b) {
+              const int jj = db + b - c;
+              const int fj = (jj >= 0) ? jj / S : -((-jj + S - 1) / S);
+              if (jj - fj * S != 0) continue;
+              const float2 rv = win[fi - DMIN][e + fj - DMIN];
+              acca = fmaf(kw[a * K + b], rv.x, acca);
+              accb = fmaf(kw[a * K + b], rv.y, accb);
+            }
           }
+          if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+          oa[e * S + db] = acca;
+          ob[e * S + db] = accb;
         }
-        if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
-        oa[db] = acca;
-        ob[db] = accb;
       }
-      const size_t off = (size_t)(my * S + da) * oW + (size_t)(mx * S);
-#pragma unroll
-      for (int db = 0; db < S; ++db) {
-        st_io<IO>(io.oa, off + db, oa[db]);
-        if (io.ob) st_io<IO>(io.ob, off + db, ob[db]);
-      }
+      const size_t off = (size_t)(my * S + da) * oW + (size_t)(mx0 * S);
+      store_run<IO, NO>(io.oa, off, oa, vec, ncell * S);
+      if (io.ob) store_run<IO, NO>(io.ob, off, ob, vec, ncell * S);
     }
   }
 }
@@ -376,12 +480,12 @@ CVB_HD void run_epilogue(int tid, int nthr, const float2* sm, const float* wk, c
                          const IoArgs& io) {
   const int key = P.s * 100 + P.k;
   switch (key) {
-    case 202: epilogue_static<2, 2, IO>(tid, nthr, sm, wk, P, io); break;
-    case 203: epilogue_static<2, 3, IO>(tid, nthr, sm, wk, P, io); break;
-    case 205: epilogue_static<2, 5, IO>(tid, nthr, sm, wk, P, io); break;
-    case 303: epilogue_static<3, 3, IO>(tid, nthr, sm, wk, P, io); break;
-    case 305: epilogue_static<3, 5, IO>(tid, nthr, sm, wk, P, io); break;
-    case 407: epilogue_static<4, 7, IO>(tid, nthr, sm, wk, P, io); break;
+    case 202: epilogue_static<2, 2, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    case 203: epilogue_static<2, 3, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    case 205: epilogue_static<2, 5, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    case 303: epilogue_static<3, 3, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    case 305: epilogue_static<3, 5, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    case 407: epilogue_static<4, 7, 2, IO>(tid, nthr, sm, wk, P, io); break;
     default: epilogue_generic<IO>(tid, nthr, sm, wk, P, io); break;
   }
 }
@@ -412,7 +516,8 @@ struct SmemLayout {
   int twy;     // h
   int twx;     // w
   int wk;      // k*k floats, rounded up to float2
-  __host__ __device__ size_t bytes() const { return (size_t)(plane + twy + twx + wk) * sizeof(float2); }
+  int maps;    // h + w ints (pad maps), rounded up to float2
+  __host__ __device__ size_t bytes() const { return (size_t)(plane + twy + twx + wk + maps) * sizeof(float2); }
 };
 CVB_HD SmemLayout smem_layout(int h, int w, int pitch, int k) {
   SmemLayout l;
@@ -420,13 +525,22 @@ CVB_HD SmemLayout smem_layout(int h, int w, int pitch, int k) {
   l.twy = h;
   l.twx = w;
   l.wk = (k * k + 1) / 2;
+  l.maps = (h + w + 1) / 2;
   return l;
 }
 
-CVB_HD void load_tables(int tid, int nthr, const FwdParams& P, int c, float2* twy, float2* twx, float* wk) {
+CVB_HD void load_tables(int tid, int nthr, const FwdParams& P, int c, float2* twy, float2* twx, float* wk,
+                        int* maps) {
   const float2* gtw = P.table + (size_t)P.C * P.h * P.w;
-  for (int i = tid; i < P.h; i += nthr) twy[i] = gtw[i];
-  for (int i = tid; i < P.w; i += nthr) twx[i] = gtw[P.h + i];
+  for (int i = tid; i < P.h; i += nthr) {
+    twy[i] = gtw[i];
+    const int ry = pad_index(i - P.p, P.H, P.pad_mode);
+    maps[i] = ry < 0 ? -1 : ry * P.W;
+  }
+  for (int i = tid; i < P.w; i += nthr) {
+    twx[i] = gtw[P.h + i];
+    maps[P.h + i] = pad_index(i - P.p, P.W, P.pad_mode);
+  }
   if (P.s > 1)
     for (int i = tid; i < P.k * P.k; i += nthr) wk[i] = P.weight[(size_t)c * P.k * P.k + i];
 }
@@ -450,6 +564,8 @@ CVB_HD IoArgs make_io(const FwdParams& P, int c, int pa, int pb) {
   io.H = P.H; io.W = P.W; io.p = P.p; io.pad_mode = P.pad_mode; io.gelu = P.fuse_gelu;
   io.h = P.h; io.w = P.w;
   io.tab = P.table + (size_t)c * P.h * P.w;
+  io.rmap = nullptr;
+  io.cmap = nullptr;
   return io;
 }
 
@@ -482,7 +598,7 @@ CVB_HD void phase_multiply(int tid, int nthr, float2* plane, const FwdParams& P,
     const float2 g = io.tab[i];
     float2* e = plane + posy * P.pitch + posx;
     const float2 v = *e;
-    *e = make_float2(fmaf(-v.y, g.y, v.x * g.x), fmaf(v.x, g.y, v.y * g.x));
+    *e = make_float2(fmaf(-v.y, g.y, v.x * g.x), -fmaf(v.x, g.y, v.y * g.x));  // conj(v * g)
   }
 }
 
@@ -511,26 +627,31 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
   float2* twy = plane + lay.plane;
   float2* twx = twy + lay.twy;
   float* wk = (float*)(twx + lay.twx);
+  int* maps = (int*)((float2*)wk + lay.wk);
   int c, pa, pb;
   pair_planes(P, pair, c, pa, pb);
-  const IoArgs io = make_io<IO>(P, c, pa, pb);
+  IoArgs io = make_io<IO>(P, c, pa, pb);
+  io.rmap = maps;
+  io.cmap = maps + P.h;
   const Plan1D& py = P.py;
   const Plan1D& px = P.px;
 
-  CVB_PHASE((load_tables(tid, nthr, P, c, twy, twx, wk), phase_load_plane<IO>(tid, nthr, plane, P, io)));
-  for (int i = 0; i < py.nst; ++i)
-    CVB_PHASE((run_pass<MODE_FWD>(py.radix[i], tid, nthr,
-                                  make_pass(plane, true, P.pitch, P.h, P.w, py.n, py.L[i], py.M[i], twy), io)));
-  for (int i = 0; i < px.nst; ++i)
-    CVB_PHASE((run_pass<MODE_FWD>(px.radix[i], tid, nthr,
-                                  make_pass(plane, false, P.pitch, P.h, P.w, px.n, px.L[i], px.M[i], twx), io)));
-  CVB_PHASE(phase_multiply(tid, nthr, plane, P, io));
-  for (int i = px.nst - 1; i >= 0; --i)
-    CVB_PHASE((run_pass<MODE_INV>(px.radix[i], tid, nthr,
-                                  make_pass(plane, false, P.pitch, P.h, P.w, px.n, px.L[i], px.M[i], twx), io)));
-  for (int i = py.nst - 1; i >= 0; --i)
-    CVB_PHASE((run_pass<MODE_INV>(py.radix[i], tid, nthr,
-                                  make_pass(plane, true, P.pitch, P.h, P.w, py.n, py.L[i], py.M[i], twy), io)));
+  CVB_PHASE((load_tables(tid, nthr, P, c, twy, twx, wk, maps), phase_load_plane<IO>(tid, nthr, plane, P, io)));
+  // One loop over all stages: forward columns, forward rows, (multiply), inverse rows, inverse columns.
+  const int nf = py.nst + px.nst;
+  for (int ph = 0; ph < 2 * nf; ++ph) {
+    const bool inv = ph >= nf;
+    const int q = inv ? 2 * nf - 1 - ph : ph;      // stage slot in forward order
+    const bool along_y = q < py.nst;
+    const Plan1D& pl = along_y ? py : px;
+    const int i = along_y ? q : q - py.nst;
+    int flags = inv ? PASS_PRE : 0;
+    if (inv && q == 0) flags |= PASS_CONJ_OUT;
+    if (ph == nf) CVB_PHASE(phase_multiply(tid, nthr, plane, P, io));
+    CVB_PHASE((run_pass<float>(pl.radix[i], tid, nthr,
+                               make_pass(plane, along_y, P.pitch, P.h, P.w, pl.n, pl.L[i], pl.M[i],
+                                         along_y ? twy : twx), io, flags)));
+  }
   if (P.s == 1) {
     CVB_PHASE(phase_store_plane<IO>(tid, nthr, plane, P, io));
   } else {
@@ -538,12 +659,29 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
   }
 }
 
-// Compile-time plan: h = RY0*RY1, w = RX0*RX1, two stages per axis, all index
-// arithmetic folded by the compiler and only the four needed butterflies in the
-// kernel's register budget.
-template <typename IO, int RY0, int RY1, int RX0, int RX1>
-__host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2* smem, int nthr_emu) {
-  (void)nthr_emu;
+// Compile-time plan: h = RY0*RY1, w = RX0*RX1, two stages per axis, NT threads; all
+// index arithmetic is folded by the compiler and only the four needed butterflies
+// count against the kernel's register budget.
+#ifdef __CUDA_ARCH__
+#define CVB_PHASE_CT(call)                               \
+  do {                                                   \
+    const int tid = threadIdx.x;                         \
+    constexpr int nthr = NT;                             \
+    call;                                                \
+    __syncthreads();                                     \
+  } while (0)
+#else
+#define CVB_PHASE_CT(call)                               \
+  do {                                                   \
+    for (int tid = 0; tid < NT; ++tid) {                 \
+      constexpr int nthr = NT;                           \
+      call;                                              \
+    }                                                    \
+  } while (0)
+#endif
+
+template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT, bool UNIFIED = false>
+__host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2* smem) {
   constexpr int h = RY0 * RY1, w = RX0 * RX1;
   constexpr int pitch = w | 1;
   const SmemLayout lay = smem_layout(h, w, pitch, P.k);
@@ -551,24 +689,70 @@ __host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2*
   float2* twy = plane + lay.plane;
   float2* twx = twy + lay.twy;
   float* wk = (float*)(twx + lay.twx);
+  int* maps = (int*)((float2*)wk + lay.wk);
   int c, pa, pb;
   pair_planes(P, pair, c, pa, pb);
   IoArgs io = make_io<IO>(P, c, pa, pb);
   io.h = h; io.w = w;
+  io.rmap = maps;
+  io.cmap = maps + h;
 
-  CVB_PHASE(load_tables(tid, nthr, P, c, twy, twx, wk));
-  CVB_PHASE((fft_pass<RY0, MODE_LOAD, IO>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
-  CVB_PHASE((fft_pass<RY1, MODE_FWD, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, RY1, 1, twy), io)));
-  CVB_PHASE((fft_pass<RX0, MODE_FWD, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, w, RX1, twx), io)));
-  CVB_PHASE((fft_pass<RX1, MODE_MID, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, RX1, 1, twx), io)));
-  CVB_PHASE((fft_pass<RX0, MODE_INV, float>(tid, nthr, make_pass(plane, false, pitch, h, w, w, w, RX1, twx), io)));
-  CVB_PHASE((fft_pass<RY1, MODE_INV, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, RY1, 1, twy), io)));
-  if (P.s == 1) {
-    CVB_PHASE((fft_pass<RY0, MODE_STORE, IO>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
-  } else {
-    CVB_PHASE((fft_pass<RY0, MODE_INV, float>(tid, nthr, make_pass(plane, true, pitch, h, w, h, h, RY1, twy), io)));
-    CVB_PHASE(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
+  CVB_PHASE_CT(load_tables(tid, nthr, P, c, twy, twx, wk, maps));
+  if constexpr (UNIFIED) {
+  // Seven stages driven by one loop, so that each of the (at most four) butterflies
+  // appears once in the kernel: columns RY0, RY1; rows RX0, RX1 (with the transfer
+  // multiply); then the inverse in the opposite order.
+  const int last = PASS_PRE | PASS_CONJ_OUT | (P.s == 1 ? PASS_DST_GLOBAL : 0);
+#pragma unroll 1
+  for (int ph = 0; ph < 7; ++ph) {
+    const int q = ph < 4 ? ph : 6 - ph;  // 0: RY0, 1: RY1, 2: RX0, 3: RX1
+    const int flags = ph == 0 ? PASS_SRC_GLOBAL : ph == 3 ? PASS_MID : ph == 6 ? last : ph > 3 ? PASS_PRE : 0;
+    if (P.skip_mask & (2 << ph)) continue;
+    const bool along_y = q < 2, first = (q & 1) == 0;
+    const PassArgs a = make_pass(plane, along_y, pitch, h, w, along_y ? h : w,
+                                 first ? (along_y ? h : w) : (along_y ? RY1 : RX1),
+                                 first ? (along_y ? RY1 : RX1) : 1, along_y ? twy : twx);
+    if constexpr (RY0 == RX0 && RY1 == RX1) {
+      // square plane: two butterflies in the whole kernel
+      if (first) {
+        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, h>(tid, nthr, a, io, flags)));
+      } else {
+        CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, h>(tid, nthr, a, io, flags)));
+      }
+    } else {
+      if (q == 0) {
+        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w>(tid, nthr, a, io, flags)));
+      } else if (q == 1) {
+        CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w>(tid, nthr, a, io, flags)));
+      } else if (q == 2) {
+        CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h>(tid, nthr, a, io, flags)));
+      } else {
+        CVB_PHASE_CT((fft_pass<RX1, IO, w, RX1, 1, h>(tid, nthr, a, io, flags)));
+      }
+    }
   }
+  } else {
+    // every stage compiled with its own flags: more code, fewer instructions executed
+    const PassArgs ay0 = make_pass(plane, true, pitch, h, w, h, h, RY1, twy);
+    const PassArgs ay1 = make_pass(plane, true, pitch, h, w, h, RY1, 1, twy);
+    const PassArgs ax0 = make_pass(plane, false, pitch, h, w, w, w, RX1, twx);
+    const PassArgs ax1 = make_pass(plane, false, pitch, h, w, w, RX1, 1, twx);
+    const int sk = P.skip_mask;
+    if (!(sk & 2)) CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_SRC_GLOBAL>(tid, nthr, ay0, io, 0)));
+    if (!(sk & 4)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, 0>(tid, nthr, ay1, io, 0)));
+    if (!(sk & 8)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, 0>(tid, nthr, ax0, io, 0)));
+    if (!(sk & 16)) CVB_PHASE_CT((fft_pass<RX1, IO, w, RX1, 1, h, PASS_MID>(tid, nthr, ax1, io, 0)));
+    if (!(sk & 32)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, PASS_PRE>(tid, nthr, ax0, io, 0)));
+    if (!(sk & 64)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, PASS_PRE>(tid, nthr, ay1, io, 0)));
+    if (!(sk & 128)) {
+      if (P.s == 1) {
+        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT | PASS_DST_GLOBAL>(tid, nthr, ay0, io, 0)));
+      } else {
+        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT>(tid, nthr, ay0, io, 0)));
+      }
+    }
+  }
+  if (P.s != 1 && !(P.skip_mask & 256)) CVB_PHASE_CT(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
 }
 
 // ---------------------------------------------------------------- transfer table

@@ -33,6 +33,7 @@ int emu_converse2d_fwd(const float* x, float* out, const void* table, const floa
   P.B = B; P.C = C; P.H = H; P.W = W; P.k = k; P.s = s; P.p = p; P.pad_mode = pad_mode;
   P.fuse_gelu = fuse_gelu;
   P.h = H + 2 * p; P.w = W + 2 * p; P.pitch = P.w | 1;
+  P.skip_mask = 0;
   if (!make_plan(P.h, P.py) || !make_plan(P.w, P.px)) return -3;
   std::vector<float2> smem(smem_bytes_for(P.h, P.w, k) / sizeof(float2) + 16);
   const int pairs = C * ((B + 1) / 2);
@@ -40,11 +41,11 @@ int emu_converse2d_fwd(const float* x, float* out, const void* table, const floa
     if (variant == 0) {
       smem_block_dynamic<float>(P, pair, smem.data(), nthr);
     } else if (P.h == 68 && P.w == 68) {
-      smem_block_static<float, 17, 4, 17, 4>(P, pair, smem.data(), nthr);
+      smem_block_static<float, 17, 4, 17, 4, 272>(P, pair, smem.data());
     } else if (P.h == 34 && P.w == 42) {
-      smem_block_static<float, 17, 2, 7, 6>(P, pair, smem.data(), nthr);
+      smem_block_static<float, 17, 2, 7, 6, 96, true>(P, pair, smem.data());
     } else if (P.h == 36 && P.w == 44) {
-      smem_block_static<float, 6, 6, 11, 4>(P, pair, smem.data(), nthr);
+      smem_block_static<float, 6, 6, 11, 4, 160>(P, pair, smem.data());
     } else {
       return -100;
     }
