@@ -8,7 +8,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libconverse_b200.so")
+LIB_PATH = os.environ.get("CVB_LIBRARY") or os.path.join(_HERE, "libconverse_b200.so")
 
 PAD_MODES = {"circular": 0, "replicate": 1, "reflect": 2, "constant": 3}
 CVB_F32, CVB_BF16 = 0, 1

@@ -54,6 +54,7 @@ struct FwdParams {
   int B, C, H, W, k, s, p, pad_mode, fuse_gelu;
   int h, w, pitch;
   int skip_mask;  // tuning aid: bit i set = phase i is not executed (results are then wrong)
+  int ystash;     // 1: shared memory also keeps the padded input (x0 of the s > 1 epilogue)
   Plan1D py, px;
 };
 
@@ -74,6 +75,8 @@ struct IoArgs {
   const float2* tab;  // this channel's multiplier
   const int* rmap;    // padded row -> source row * W, or -1 (zero)
   const int* cmap;    // padded column -> source column, or -1 (zero)
+  float2* ycopy;      // padded input of both planes, same layout as the FFT plane; null if not kept
+  int yoff;           // ycopy - plane, in float2 units
 };
 
 // ---------------------------------------------------------------- helpers
@@ -191,6 +194,10 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
         re[q] = va;
         im[q] = vb;
       }
+      if (io.ycopy) {  // after all loads are in flight
+#pragma unroll
+        for (int q = 0; q < R; ++q) ptr[io.yoff + q * st] = make_float2(re[q], im[q]);
+      }
     } else {
 #pragma unroll
       for (int q = 0; q < R; ++q) {
@@ -304,8 +311,14 @@ CVB_HD void epilogue_generic(int tid, int nthr, const float2* sm, const float* w
     int my, mx;
     divmod_small(ci, P.W, invW, my, mx);
     const size_t xoff = (size_t)my * P.W + mx;
-    const float ya = ld_io<IO>(io.xa, xoff);
-    const float yb = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
+    float ya, yb;
+    if (io.ycopy) {
+      const float2 v = io.ycopy[(my + p) * P.pitch + mx + p];
+      ya = v.x; yb = v.y;
+    } else {
+      ya = ld_io<IO>(io.xa, xoff);
+      yb = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
+    }
     const int m = my + p, n = mx + p;
     for (int da = 0; da < s; ++da) {
       for (int db = 0; db < s; ++db) {
@@ -386,42 +399,42 @@ template <> CVB_HD void store_run<__nv_bfloat16, 12>(void* b, size_t o, const fl
 template <> CVB_HD void store_run<__nv_bfloat16, 16>(void* b, size_t o, const float (&v)[16], bool vec, int n) { store_run_bf16<16>(b, o, v, vec, n); }
 
 // Compile-time (S, K): the taps each output phase touches are resolved by the
-// compiler.  A thread owns a strip of CW low-resolution cells of one row: the r
-// window (WIN rows x CW+WIN-1 columns) is loaded once, each of the S output rows
-// leaves as one run of CW*S values.
-template <int S, int K, int CW, typename IO>
-CVB_HD void epilogue_static(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
-                            const IoArgs& io) {
+// compiler.  A thread owns a strip of CW low-resolution columns and walks down a
+// segment of rows with a sliding window of r (WIN rows x CW+WIN-1 columns): one new
+// window row is read per step, and each of the S output rows of the step leaves as
+// one run of CW*S values (16 bytes per lane, consecutive lanes = consecutive strips).
+template <int S, int K, int CW, typename IO, bool GELU>
+CVB_HD void epilogue_rows(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
+                          const IoArgs& io) {
   constexpr int c = K / 2;
   constexpr int DMIN = (c == 0) ? 0 : -((c + S - 1) / S);
   constexpr int DMAX = (S - 1 + K - 1 - c) / S;
   constexpr int WIN = DMAX - DMIN + 1;
   constexpr int WC = CW + WIN - 1;
   constexpr int NO = CW * S;
-  const int p = P.p, h = P.h, w = P.w;
+  constexpr int VEC = sizeof(IO) == 4 ? 4 : 8;  // elements per 16-byte store
+  const int p = P.p, h = P.h, w = P.w, pitch = P.pitch;
   const int spr = (P.W + CW - 1) / CW;  // strips per row
-  const int nstrips = P.H * spr;
+  int nseg = nthr / spr;                // row segments handled concurrently
+  if (nseg < 1) nseg = 1;
+  if (nseg > P.H) nseg = P.H;
+  const int rps = (P.H + nseg - 1) / nseg;  // rows per segment
+  const int nitems = nseg * spr;
   const int oW = P.W * S;
   const float inv_spr = 1.0f / (float)spr;
-  constexpr int VEC = sizeof(IO) == 4 ? 4 : 8;  // elements per 16-byte store
   const bool vec = (P.W % CW == 0) && (NO % VEC == 0) && (oW % VEC == 0) &&
                    (((size_t)io.oa) % 16 == 0) && (((size_t)io.ob) % 16 == 0);
+  const bool nost = (P.skip_mask & 512) != 0;  // tuning aid: compute but do not store
   float kw[K * K];
 #pragma unroll
   for (int i = 0; i < K * K; ++i) kw[i] = wk[i];
-  for (int si = tid; si < nstrips; si += nthr) {
-    int my, sx;
-    divmod_small(si, spr, inv_spr, my, sx);
+  for (int it = tid; it < nitems; it += nthr) {
+    int seg, sx;
+    divmod_small(it, spr, inv_spr, seg, sx);
     const int mx0 = sx * CW;
     const int ncell = (P.W - mx0) < CW ? (P.W - mx0) : CW;
-    float ya[CW], yb[CW];
-#pragma unroll
-    for (int e = 0; e < CW; ++e) {
-      const size_t xoff = (size_t)my * P.W + (mx0 + (e < ncell ? e : 0));
-      ya[e] = ld_io<IO>(io.xa, xoff);
-      yb[e] = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
-    }
-    float2 win[WIN][WC];
+    const int my_begin = seg * rps;
+    const int my_end = (my_begin + rps) < P.H ? (my_begin + rps) : P.H;
     int cols[WC];
 #pragma unroll
     for (int e = 0; e < WC; ++e) {
@@ -431,48 +444,85 @@ CVB_HD void epilogue_static(int tid, int nthr, const float2* sm, const float* wk
       if (rn >= w) rn -= w;
       cols[e] = rn;
     }
+    // window rows my + p + DMIN .. my + p + DMAX; preload all but the last
+    float2 win[WIN][WC];
+    int rm = my_begin + p + DMIN;
+    if (rm < 0) rm += h;
+    if (rm >= h) rm -= h;
 #pragma unroll
-    for (int d = 0; d < WIN; ++d) {
-      int rm = my + p + DMIN + d;
-      if (rm < 0) rm += h;
-      if (rm >= h) rm -= h;
-      const float2* rowp = sm + rm * P.pitch;
+    for (int d = 0; d + 1 < WIN; ++d) {
 #pragma unroll
-      for (int e = 0; e < WC; ++e) win[d][e] = rowp[cols[e]];
+      for (int e = 0; e < WC; ++e) win[d][e] = sm[rm * pitch + cols[e]];
+      rm = (rm + 1 == h) ? 0 : rm + 1;
     }
+    for (int my = my_begin; my < my_end; ++my) {
 #pragma unroll
-    for (int da = 0; da < S; ++da) {
-      float oa[NO], ob[NO];
+      for (int e = 0; e < WC; ++e) win[WIN - 1][e] = sm[rm * pitch + cols[e]];
+      rm = (rm + 1 == h) ? 0 : rm + 1;
+      float ya[CW], yb[CW];
+      if (io.ycopy) {
+        const float2* yrow = io.ycopy + (my + p) * pitch + mx0 + p;
 #pragma unroll
-      for (int e = 0; e < CW; ++e) {
+        for (int e = 0; e < CW; ++e) {
+          const float2 v = yrow[e < ncell ? e : 0];
+          ya[e] = v.x;
+          yb[e] = v.y;
+        }
+      } else {
 #pragma unroll
-        for (int db = 0; db < S; ++db) {
-          float acca = ya[e], accb = yb[e];
-#pragma unroll
-          for (int a = 0; a < K; ++a) {
-            const int ii = da + a - c;
-            const int fi = (ii >= 0) ? ii / S : -((-ii + S - 1) / S);
-            if (ii - fi * S != 0) continue;
-#pragma unroll
-            for (int b = 0; b < K; ++b) {
-              const int jj = db + b - c;
-              const int fj = (jj >= 0) ? jj / S : -((-jj + S - 1) / S);
-              if (jj - fj * S != 0) continue;
-              const float2 rv = win[fi - DMIN][e + fj - DMIN];
-              acca = fmaf(kw[a * K + b], rv.x, acca);
-              accb = fmaf(kw[a * K + b], rv.y, accb);
-            }
-          }
-          if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
-          oa[e * S + db] = acca;
-          ob[e * S + db] = accb;
+        for (int e = 0; e < CW; ++e) {
+          const size_t xoff = (size_t)my * P.W + (mx0 + (e < ncell ? e : 0));
+          ya[e] = ld_io<IO>(io.xa, xoff);
+          yb[e] = io.xb ? ld_io<IO>(io.xb, xoff) : 0.f;
         }
       }
-      const size_t off = (size_t)(my * S + da) * oW + (size_t)(mx0 * S);
-      store_run<IO, NO>(io.oa, off, oa, vec, ncell * S);
-      if (io.ob) store_run<IO, NO>(io.ob, off, ob, vec, ncell * S);
+#pragma unroll
+      for (int da = 0; da < S; ++da) {
+        float oa[NO], ob[NO];
+#pragma unroll
+        for (int e = 0; e < CW; ++e) {
+#pragma unroll
+          for (int db = 0; db < S; ++db) {
+            float acca = ya[e], accb = yb[e];
+#pragma unroll
+            for (int a = 0; a < K; ++a) {
+              const int ii = da + a - c;
+              const int fi = (ii >= 0) ? ii / S : -((-ii + S - 1) / S);
+              if (ii - fi * S != 0) continue;
+#pragma unroll
+              for (int b = 0; b < K; ++b) {
+                const int jj = db + b - c;
+                const int fj = (jj >= 0) ? jj / S : -((-jj + S - 1) / S);
+                if (jj - fj * S != 0) continue;
+                const float2 rv = win[fi - DMIN][e + fj - DMIN];
+                acca = fmaf(kw[a * K + b], rv.x, acca);
+                accb = fmaf(kw[a * K + b], rv.y, accb);
+              }
+            }
+            if (GELU) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+            oa[e * S + db] = acca;
+            ob[e * S + db] = accb;
+          }
+        }
+        const size_t off = (size_t)(my * S + da) * oW + (size_t)(mx0 * S);
+        store_run<IO, NO>(io.oa, off, oa, vec && !nost, nost ? 0 : ncell * S);
+        if (io.ob) store_run<IO, NO>(io.ob, off, ob, vec && !nost, nost ? 0 : ncell * S);
+      }
+      // slide the window down one row
+#pragma unroll
+      for (int d = 0; d + 1 < WIN; ++d) {
+#pragma unroll
+        for (int e = 0; e < WC; ++e) win[d][e] = win[d + 1][e];
+      }
     }
   }
+}
+
+template <int S, int K, int CW, typename IO>
+CVB_HD void epilogue_static(int tid, int nthr, const float2* sm, const float* wk, const FwdParams& P,
+                            const IoArgs& io) {
+  if (io.gelu) epilogue_rows<S, K, CW, IO, true>(tid, nthr, sm, wk, P, io);
+  else epilogue_rows<S, K, CW, IO, false>(tid, nthr, sm, wk, P, io);
 }
 
 template <typename IO>
@@ -480,12 +530,14 @@ CVB_HD void run_epilogue(int tid, int nthr, const float2* sm, const float* wk, c
                          const IoArgs& io) {
   const int key = P.s * 100 + P.k;
   switch (key) {
-    case 202: epilogue_static<2, 2, 4, IO>(tid, nthr, sm, wk, P, io); break;
-    case 203: epilogue_static<2, 3, 4, IO>(tid, nthr, sm, wk, P, io); break;
-    case 205: epilogue_static<2, 5, 4, IO>(tid, nthr, sm, wk, P, io); break;
+    // CW cells per thread: CW * S outputs = 16 bytes, so that a warp's store covers
+    // consecutive 16-byte pieces of one output row
+    case 202: epilogue_static<2, 2, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
+    case 203: epilogue_static<2, 3, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
+    case 205: epilogue_static<2, 5, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
     case 303: epilogue_static<3, 3, 4, IO>(tid, nthr, sm, wk, P, io); break;
     case 305: epilogue_static<3, 5, 4, IO>(tid, nthr, sm, wk, P, io); break;
-    case 407: epilogue_static<4, 7, 2, IO>(tid, nthr, sm, wk, P, io); break;
+    case 407: epilogue_static<4, 7, (sizeof(IO) == 4 ? 1 : 2), IO>(tid, nthr, sm, wk, P, io); break;
     default: epilogue_generic<IO>(tid, nthr, sm, wk, P, io); break;
   }
 }
@@ -517,15 +569,19 @@ struct SmemLayout {
   int twx;     // w
   int wk;      // k*k floats, rounded up to float2
   int maps;    // h + w ints (pad maps), rounded up to float2
-  __host__ __device__ size_t bytes() const { return (size_t)(plane + twy + twx + wk + maps) * sizeof(float2); }
+  int ycopy;   // h * pitch when the padded input is kept, else 0
+  __host__ __device__ size_t bytes() const {
+    return (size_t)(plane + twy + twx + wk + maps + ycopy) * sizeof(float2);
+  }
 };
-CVB_HD SmemLayout smem_layout(int h, int w, int pitch, int k) {
+CVB_HD SmemLayout smem_layout(int h, int w, int pitch, int k, int ystash) {
   SmemLayout l;
   l.plane = h * pitch;
   l.twy = h;
   l.twx = w;
   l.wk = (k * k + 1) / 2;
   l.maps = (h + w + 1) / 2;
+  l.ycopy = ystash ? h * pitch : 0;
   return l;
 }
 
@@ -566,6 +622,8 @@ CVB_HD IoArgs make_io(const FwdParams& P, int c, int pa, int pb) {
   io.tab = P.table + (size_t)c * P.h * P.w;
   io.rmap = nullptr;
   io.cmap = nullptr;
+  io.ycopy = nullptr;
+  io.yoff = 0;
   return io;
 }
 
@@ -586,6 +644,7 @@ CVB_HD void phase_load_plane(int tid, int nthr, float2* plane, const FwdParams& 
       if (io.xb) vb = ld_io<IO>(io.xb, off);
     }
     plane[row * P.pitch + col] = make_float2(va, vb);
+    if (io.ycopy) io.ycopy[row * P.pitch + col] = make_float2(va, vb);
   }
 }
 
@@ -622,7 +681,7 @@ CVB_HD void phase_store_plane(int tid, int nthr, const float2* plane, const FwdP
 template <typename IO>
 __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2* smem, int nthr_emu) {
   (void)nthr_emu;
-  const SmemLayout lay = smem_layout(P.h, P.w, P.pitch, P.k);
+  const SmemLayout lay = smem_layout(P.h, P.w, P.pitch, P.k, P.ystash);
   float2* plane = smem;
   float2* twy = plane + lay.plane;
   float2* twx = twy + lay.twy;
@@ -633,6 +692,7 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
   IoArgs io = make_io<IO>(P, c, pa, pb);
   io.rmap = maps;
   io.cmap = maps + P.h;
+  if (P.ystash) { io.ycopy = (float2*)maps + lay.maps; io.yoff = (int)(io.ycopy - plane); }
   const Plan1D& py = P.py;
   const Plan1D& px = P.px;
 
@@ -684,7 +744,7 @@ template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT, bool UNIFIED 
 __host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2* smem) {
   constexpr int h = RY0 * RY1, w = RX0 * RX1;
   constexpr int pitch = w | 1;
-  const SmemLayout lay = smem_layout(h, w, pitch, P.k);
+  const SmemLayout lay = smem_layout(h, w, pitch, P.k, P.ystash);
   float2* plane = smem;
   float2* twy = plane + lay.plane;
   float2* twx = twy + lay.twy;
@@ -696,6 +756,7 @@ __host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2*
   io.h = h; io.w = w;
   io.rmap = maps;
   io.cmap = maps + h;
+  if (P.ystash) { io.ycopy = (float2*)maps + lay.maps; io.yoff = (int)(io.ycopy - plane); }
 
   CVB_PHASE_CT(load_tables(tid, nthr, P, c, twy, twx, wk, maps));
   if constexpr (UNIFIED) {

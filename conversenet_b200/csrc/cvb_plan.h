@@ -54,8 +54,15 @@ inline bool make_plan(int n, Plan1D& pl) {
   return true;
 }
 
-inline size_t smem_bytes_for(int h, int w, int k) {
-  return smem_layout(h, w, w | 1, k).bytes();
+inline size_t smem_bytes_for(int h, int w, int k, int ystash = 0) {
+  return smem_layout(h, w, w | 1, k, ystash).bytes();
+}
+
+// Keep the padded input in shared memory for the s > 1 epilogue when two blocks
+// per SM still fit with it (otherwise the epilogue re-reads x through L2).
+inline int choose_ystash(int h, int w, int k, int s) {
+  if (s <= 1) return 0;
+  return smem_bytes_for(h, w, k, 1) <= kSmemLimit / 2 ? 1 : 0;
 }
 
 

@@ -34,8 +34,10 @@ int emu_converse2d_fwd(const float* x, float* out, const void* table, const floa
   P.fuse_gelu = fuse_gelu;
   P.h = H + 2 * p; P.w = W + 2 * p; P.pitch = P.w | 1;
   P.skip_mask = 0;
+  P.ystash = (variant & 2) ? 0 : choose_ystash(P.h, P.w, k, s);
+  variant &= 1;
   if (!make_plan(P.h, P.py) || !make_plan(P.w, P.px)) return -3;
-  std::vector<float2> smem(smem_bytes_for(P.h, P.w, k) / sizeof(float2) + 16);
+  std::vector<float2> smem(smem_bytes_for(P.h, P.w, k, 1) / sizeof(float2) + 16);
   const int pairs = C * ((B + 1) / 2);
   for (int pair = 0; pair < pairs; ++pair) {
     if (variant == 0) {

@@ -64,7 +64,7 @@ def test_emu_static_plan_body(emu, shape, k, s, p, mode):
     w, b = orc.init_weight(shape[1], k, rng)
     b = (9.0 + rng.standard_normal(b.shape)).astype(np.float32)
     ref = orc.converse2d_forward(x, w, b, s, p, mode, 1e-5, dtype=np.float64)
-    for variant in (0, 1):
+    for variant in (0, 1, 2, 3):  # bit 0: compile-time plan body, bit 1: epilogue re-reads x instead of shared memory
         out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=160, variant=variant)
         assert orc.rel_l2(out, ref) <= 2e-5, variant
 
