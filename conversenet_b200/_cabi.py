@@ -19,6 +19,7 @@ SIGNATURES = {
     "cvb_version": (_c.c_int, []),
     "cvb_strerror": (_c.c_char_p, [_c.c_int]),
     "cvb_last_cuda_error": (_c.c_int, []),
+    "cvb_last_device_status": (_c.c_int, [_c.c_int]),
     "cvb_transfer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int, _c.c_int]),
     "cvb_build_transfer": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                       _c.c_int, _c.c_float, _c.c_void_p, _c.c_void_p]),

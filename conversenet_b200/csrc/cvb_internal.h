@@ -22,10 +22,11 @@ inline int num_pairs(const FwdParams& P) { return P.C * ((P.B + 1) / 2); }
 int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
 
 // Compile-time-plan kernels (k_static.cu, one object per registry line).
-typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
+typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, int blocks, cudaStream_t st);
 struct StaticEntry {
-  int ry0, ry1, rx0, rx1;
-  StaticLauncher fn;
+  int ry0, ry1, rx0, rx1, nt, mb;
+  StaticLauncher fn;          // one block per plane pair
+  StaticLauncher fn_persist;  // persistent blocks with prefetch
 };
 
 }  // namespace cvb

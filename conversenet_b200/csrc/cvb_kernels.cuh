@@ -32,6 +32,7 @@
 
 #define CVB_HD __host__ __device__ __forceinline__
 #include "fft_codelets.cuh"
+#include "cvb_tma.cuh"
 
 namespace cvb {
 
@@ -55,6 +56,7 @@ struct FwdParams {
   int h, w, pitch;
   int skip_mask;  // tuning aid: bit i set = phase i is not executed (results are then wrong)
   int ystash;     // 1: shared memory also keeps the padded input (x0 of the s > 1 epilogue)
+  int* status;    // device word set non-zero when a bounded wait gives up; may be null
   Plan1D py, px;
 };
 
@@ -82,18 +84,10 @@ struct IoArgs {
 // ---------------------------------------------------------------- helpers
 template <typename IO> CVB_HD float ld_io(const void* p, size_t i);
 template <> CVB_HD float ld_io<float>(const void* p, size_t i) {
-#ifdef __CUDA_ARCH__
-  return __ldg((const float*)p + i);
-#else
   return ((const float*)p)[i];
-#endif
 }
 template <> CVB_HD float ld_io<__nv_bfloat16>(const void* p, size_t i) {
-#ifdef __CUDA_ARCH__
-  return __bfloat162float(__ldg((const __nv_bfloat16*)p + i));
-#else
   return __bfloat162float(((const __nv_bfloat16*)p)[i]);
-#endif
 }
 template <typename IO> CVB_HD void st_io(void* p, size_t i, float v);
 template <> CVB_HD void st_io<float>(void* p, size_t i, float v) { ((float*)p)[i] = v; }
@@ -740,7 +734,37 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
   } while (0)
 #endif
 
-template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT, bool UNIFIED = false>
+// The seven FFT stages and the epilogue of one plane pair, every stage compiled with
+// its own flags.  `io.xa/xb` may point to global memory or to a staged copy in shared
+// memory; the stage code is the same.
+template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT>
+CVB_HD void static_stages(const FwdParams& P, const IoArgs& io, float2* plane, const float2* twy,
+                          const float2* twx, const float* wk) {
+  constexpr int h = RY0 * RY1, w = RX0 * RX1;
+  constexpr int pitch = w | 1;
+  const PassArgs ay0 = make_pass(plane, true, pitch, h, w, h, h, RY1, twy);
+  const PassArgs ay1 = make_pass(plane, true, pitch, h, w, h, RY1, 1, twy);
+  const PassArgs ax0 = make_pass(plane, false, pitch, h, w, w, w, RX1, twx);
+  const PassArgs ax1 = make_pass(plane, false, pitch, h, w, w, RX1, 1, twx);
+  const int sk = P.skip_mask;
+  if (!(sk & 2)) CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_SRC_GLOBAL>(tid, nthr, ay0, io, 0)));
+  if (!(sk & 4)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, 0>(tid, nthr, ay1, io, 0)));
+  if (!(sk & 8)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, 0>(tid, nthr, ax0, io, 0)));
+  if (!(sk & 16)) CVB_PHASE_CT((fft_pass<RX1, IO, w, RX1, 1, h, PASS_MID>(tid, nthr, ax1, io, 0)));
+  if (!(sk & 32)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, PASS_PRE>(tid, nthr, ax0, io, 0)));
+  if (!(sk & 64)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, PASS_PRE>(tid, nthr, ay1, io, 0)));
+  if (!(sk & 128)) {
+    if (P.s == 1) {
+      CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT | PASS_DST_GLOBAL>(tid, nthr, ay0, io, 0)));
+    } else {
+      CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT>(tid, nthr, ay0, io, 0)));
+    }
+  }
+  if (P.s != 1 && !(sk & 256)) CVB_PHASE_CT(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
+}
+
+// One block = one plane pair.
+template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT>
 __host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2* smem) {
   constexpr int h = RY0 * RY1, w = RX0 * RX1;
   constexpr int pitch = w | 1;
@@ -757,63 +781,102 @@ __host__ __device__ void smem_block_static(const FwdParams& P, int pair, float2*
   io.rmap = maps;
   io.cmap = maps + h;
   if (P.ystash) { io.ycopy = (float2*)maps + lay.maps; io.yoff = (int)(io.ycopy - plane); }
-
   CVB_PHASE_CT(load_tables(tid, nthr, P, c, twy, twx, wk, maps));
-  if constexpr (UNIFIED) {
-  // Seven stages driven by one loop, so that each of the (at most four) butterflies
-  // appears once in the kernel: columns RY0, RY1; rows RX0, RX1 (with the transfer
-  // multiply); then the inverse in the opposite order.
-  const int last = PASS_PRE | PASS_CONJ_OUT | (P.s == 1 ? PASS_DST_GLOBAL : 0);
-#pragma unroll 1
-  for (int ph = 0; ph < 7; ++ph) {
-    const int q = ph < 4 ? ph : 6 - ph;  // 0: RY0, 1: RY1, 2: RX0, 3: RX1
-    const int flags = ph == 0 ? PASS_SRC_GLOBAL : ph == 3 ? PASS_MID : ph == 6 ? last : ph > 3 ? PASS_PRE : 0;
-    if (P.skip_mask & (2 << ph)) continue;
-    const bool along_y = q < 2, first = (q & 1) == 0;
-    const PassArgs a = make_pass(plane, along_y, pitch, h, w, along_y ? h : w,
-                                 first ? (along_y ? h : w) : (along_y ? RY1 : RX1),
-                                 first ? (along_y ? RY1 : RX1) : 1, along_y ? twy : twx);
-    if constexpr (RY0 == RX0 && RY1 == RX1) {
-      // square plane: two butterflies in the whole kernel
-      if (first) {
-        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, h>(tid, nthr, a, io, flags)));
-      } else {
-        CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, h>(tid, nthr, a, io, flags)));
-      }
-    } else {
-      if (q == 0) {
-        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w>(tid, nthr, a, io, flags)));
-      } else if (q == 1) {
-        CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w>(tid, nthr, a, io, flags)));
-      } else if (q == 2) {
-        CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h>(tid, nthr, a, io, flags)));
-      } else {
-        CVB_PHASE_CT((fft_pass<RX1, IO, w, RX1, 1, h>(tid, nthr, a, io, flags)));
+  static_stages<IO, RY0, RY1, RX0, RX1, NT>(P, io, plane, twy, twx, wk);
+}
+
+// Persistent variant: a block loops over plane pairs (pair = block, block + nblocks, ...).
+// The raw planes of the NEXT pair are fetched by bulk asynchronous copies (TMA) into one
+// half of a double buffer while the current pair is transformed, so no thread ever
+// waits on HBM latency, and the stores of one pair drain while the next is computed.
+// The first column stage and the epilogue read x from the staged copy.
+constexpr int kWaitLimit = 1 << 18;  // polls of mbarrier.try_wait before giving up
+
+CVB_HD size_t persistent_xin_bytes(int H, int W, int esize) {
+  return ((size_t)2 * H * W * esize + 127) / 128 * 128;
+}
+CVB_HD size_t persistent_smem_bytes(int h, int w, int H, int W, int k, int esize) {
+  return 2 * persistent_xin_bytes(H, W, esize) + smem_layout(h, w, w | 1, k, 0).bytes() + 2 * sizeof(uint64_t);
+}
+
+template <typename IO>
+CVB_HD void persistent_issue(const FwdParams& P, int pair, IO* dst, uint64_t* bar) {
+  int c, pa, pb;
+  pair_planes(P, pair, c, pa, pb);
+  const size_t HW = (size_t)P.H * P.W;
+  const uint32_t bytes = (uint32_t)(HW * sizeof(IO));
+  mbar_expect_tx(bar, pb >= 0 ? 2 * bytes : bytes);
+  bulk_g2s(dst, (const IO*)P.x + (size_t)pa * HW, bytes, bar);
+  if (pb >= 0) bulk_g2s(dst + HW, (const IO*)P.x + (size_t)pb * HW, bytes, bar);
+}
+
+template <typename IO, int RY0, int RY1, int RX0, int RX1, int NT>
+__host__ __device__ void smem_persistent_static(const FwdParams& P, unsigned char* smem, int block, int nblocks) {
+  constexpr int h = RY0 * RY1, w = RX0 * RX1;
+  constexpr int pitch = w | 1;
+  const size_t HW = (size_t)P.H * P.W;
+  const size_t xin_bytes = persistent_xin_bytes(P.H, P.W, (int)sizeof(IO));
+  IO* xin0 = (IO*)smem;
+  IO* xin1 = (IO*)(smem + xin_bytes);
+  const SmemLayout lay = smem_layout(h, w, pitch, P.k, 0);
+  float2* plane = (float2*)(smem + 2 * xin_bytes);
+  float2* twy = plane + lay.plane;
+  float2* twx = twy + lay.twy;
+  float* wk = (float*)(twx + lay.twx);
+  int* maps = (int*)((float2*)wk + lay.wk);
+  uint64_t* mbar = (uint64_t*)((float2*)maps + lay.maps);
+  const int npairs = P.C * ((P.B + 1) / 2);
+  if (block >= npairs) return;
+
+#ifdef __CUDA_ARCH__
+  if (threadIdx.x == 0) {
+    mbar_init(&mbar[0], 1);
+    mbar_init(&mbar[1], 1);
+    mbar_fence_init();
+    persistent_issue<IO>(P, block, xin0, &mbar[0]);
+  }
+#else
+  persistent_issue<IO>(P, block, xin0, &mbar[0]);
+#endif
+  CVB_PHASE_CT(load_tables(tid, nthr, P, 0, twy, twx, wk, maps));
+
+  int it = 0;
+  for (int pair = block; pair < npairs; pair += nblocks, ++it) {
+    const int buf = it & 1;
+    const uint32_t parity = (uint32_t)((it >> 1) & 1);
+    IO* cur = buf ? xin1 : xin0;
+    IO* nxt = buf ? xin0 : xin1;
+    int c, pa, pb;
+    pair_planes(P, pair, c, pa, pb);
+    IoArgs io = make_io<IO>(P, c, pa, pb);
+    io.h = h; io.w = w;
+    io.rmap = maps;
+    io.cmap = maps + h;
+    io.xa = cur;
+    io.xb = pb >= 0 ? (const void*)(cur + HW) : nullptr;
+    const bool more = pair + nblocks < npairs;
+#ifdef __CUDA_ARCH__
+    {
+      const int tid = threadIdx.x;
+      // the other half was last read in the previous iteration, which ended with a barrier
+      if (tid == 0 && more) persistent_issue<IO>(P, pair + nblocks, nxt, &mbar[buf ^ 1]);
+      if (P.s > 1)
+        for (int i = tid; i < P.k * P.k; i += NT) wk[i] = P.weight[(size_t)c * P.k * P.k + i];
+      const bool ok = mbar_wait_bounded(&mbar[buf], parity, kWaitLimit);
+      if (__syncthreads_or(!ok)) {
+        // give up: flag it, let the copy in flight (if any) land, and leave
+        if (tid == 0 && P.status) atomicExch(P.status, 1);
+        if (more) mbar_wait_bounded(&mbar[buf ^ 1], (uint32_t)(((it + 1) >> 1) & 1), kWaitLimit);
+        return;
       }
     }
+#else
+    if (more) persistent_issue<IO>(P, pair + nblocks, nxt, &mbar[buf ^ 1]);
+    if (P.s > 1)
+      for (int i = 0; i < P.k * P.k; ++i) wk[i] = P.weight[(size_t)c * P.k * P.k + i];
+#endif
+    static_stages<IO, RY0, RY1, RX0, RX1, NT>(P, io, plane, twy, twx, wk);
   }
-  } else {
-    // every stage compiled with its own flags: more code, fewer instructions executed
-    const PassArgs ay0 = make_pass(plane, true, pitch, h, w, h, h, RY1, twy);
-    const PassArgs ay1 = make_pass(plane, true, pitch, h, w, h, RY1, 1, twy);
-    const PassArgs ax0 = make_pass(plane, false, pitch, h, w, w, w, RX1, twx);
-    const PassArgs ax1 = make_pass(plane, false, pitch, h, w, w, RX1, 1, twx);
-    const int sk = P.skip_mask;
-    if (!(sk & 2)) CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_SRC_GLOBAL>(tid, nthr, ay0, io, 0)));
-    if (!(sk & 4)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, 0>(tid, nthr, ay1, io, 0)));
-    if (!(sk & 8)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, 0>(tid, nthr, ax0, io, 0)));
-    if (!(sk & 16)) CVB_PHASE_CT((fft_pass<RX1, IO, w, RX1, 1, h, PASS_MID>(tid, nthr, ax1, io, 0)));
-    if (!(sk & 32)) CVB_PHASE_CT((fft_pass<RX0, IO, w, w, RX1, h, PASS_PRE>(tid, nthr, ax0, io, 0)));
-    if (!(sk & 64)) CVB_PHASE_CT((fft_pass<RY1, IO, h, RY1, 1, w, PASS_PRE>(tid, nthr, ay1, io, 0)));
-    if (!(sk & 128)) {
-      if (P.s == 1) {
-        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT | PASS_DST_GLOBAL>(tid, nthr, ay0, io, 0)));
-      } else {
-        CVB_PHASE_CT((fft_pass<RY0, IO, h, h, RY1, w, PASS_PRE | PASS_CONJ_OUT>(tid, nthr, ay0, io, 0)));
-      }
-    }
-  }
-  if (P.s != 1 && !(P.skip_mask & 256)) CVB_PHASE_CT(run_epilogue<IO>(tid, nthr, plane, wk, P, io));
 }
 
 // ---------------------------------------------------------------- transfer table

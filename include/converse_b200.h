@@ -52,6 +52,14 @@ const char* cvb_strerror(int status);
 int cvb_last_cuda_error(void);
 
 /*
+ * Device-side status of the current device: 0, or non-zero after a kernel gave up a
+ * bounded wait (its output is then incomplete).  Synchronises the device; clears the
+ * word when `clear` is non-zero.  Negative on a runtime error.  (The reference has no
+ * counterpart: its op only raises host-side c10::Error, converse2d.cpp:167-172.)
+ */
+int cvb_last_device_status(int clear);
+
+/*
  * Size in bytes of the transfer table for C channels (or B*C planes when the
  * kernels differ per sample) at padded size h x w = (H+2p) x (W+2p).
  * Replaces the FB/FBC/F2B triple the reference caches per weight tensor

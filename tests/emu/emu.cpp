@@ -35,17 +35,26 @@ int emu_converse2d_fwd(const float* x, float* out, const void* table, const floa
   P.h = H + 2 * p; P.w = W + 2 * p; P.pitch = P.w | 1;
   P.skip_mask = 0;
   P.ystash = (variant & 2) ? 0 : choose_ystash(P.h, P.w, k, s);
-  variant &= 1;
   if (!make_plan(P.h, P.py) || !make_plan(P.w, P.px)) return -3;
   std::vector<float2> smem(smem_bytes_for(P.h, P.w, k, 1) / sizeof(float2) + 16);
   const int pairs = C * ((B + 1) / 2);
+  P.status = nullptr;
+  if (variant & 4) {
+    // persistent body: 3 emulated blocks share the pairs round-robin
+    if (!(P.h == 68 && P.w == 68)) return -100;
+    P.ystash = 0;
+    std::vector<unsigned char> ps(persistent_smem_bytes(P.h, P.w, H, W, k, 4) + 256);
+    unsigned char* base = (unsigned char*)(((size_t)ps.data() + 127) / 128 * 128);
+    for (int b = 0; b < 3; ++b) smem_persistent_static<float, 17, 4, 17, 4, 272>(P, base, b, 3);
+    return 0;
+  }
   for (int pair = 0; pair < pairs; ++pair) {
-    if (variant == 0) {
+    if ((variant & 1) == 0) {
       smem_block_dynamic<float>(P, pair, smem.data(), nthr);
     } else if (P.h == 68 && P.w == 68) {
       smem_block_static<float, 17, 4, 17, 4, 272>(P, pair, smem.data());
     } else if (P.h == 34 && P.w == 42) {
-      smem_block_static<float, 17, 2, 7, 6, 96, true>(P, pair, smem.data());
+      smem_block_static<float, 17, 2, 7, 6, 96>(P, pair, smem.data());
     } else if (P.h == 36 && P.w == 44) {
       smem_block_static<float, 6, 6, 11, 4, 160>(P, pair, smem.data());
     } else {

@@ -94,6 +94,23 @@ def test_forced_runtime_plan_matches_compiled_plan(monkeypatch):
     assert orc.rel_l2(a, d) <= 2e-6
 
 
+def test_persistent_prefetch_kernel_matches(monkeypatch):
+    # blocks looping over plane pairs with bulk-copy (TMA) prefetch of x; bounded waits must not trip
+    from conversenet_b200 import _cabi
+    cfg = dict(CONFIGS["cfg2"], B=12)
+    x, w, b = _seeded(cfg, 21)
+    base = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    monkeypatch.setenv("CVB_PERSIST", "1")
+    pers = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    assert _cabi.load().cvb_last_device_status(1) == 0
+    assert orc.rel_l2(pers, base) <= 1e-6
+    pers1 = _run(x, w, b, 1, cfg["p"], cfg["mode"], cfg["eps"])
+    monkeypatch.setenv("CVB_PERSIST", "0")
+    base1 = _run(x, w, b, 1, cfg["p"], cfg["mode"], cfg["eps"])
+    assert _cabi.load().cvb_last_device_status(1) == 0
+    assert orc.rel_l2(pers1, base1) <= 1e-6
+
+
 def test_linearity_and_constant_planes_full_size():
     # size-independent properties at the bench workload's full size
     cfg = CONFIGS["cfg2"]

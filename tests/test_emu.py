@@ -69,6 +69,17 @@ def test_emu_static_plan_body(emu, shape, k, s, p, mode):
         assert orc.rel_l2(out, ref) <= 2e-5, variant
 
 
+@pytest.mark.parametrize("B,s", [(5, 2), (4, 1), (7, 2)])
+def test_emu_persistent_body(emu, B, s):
+    # blocks loop over plane pairs with the double-buffered staging of x (copies emulated by memcpy)
+    rng = np.random.default_rng(B)
+    x = rng.standard_normal((B, 3, 64, 64)).astype(np.float32)
+    w, b = orc.init_weight(3, 5, rng)
+    ref = orc.converse2d_forward(x, w, b, s, 2, "replicate", 1e-5, dtype=np.float64)
+    out = emu_forward(emu, x, w, b, s, 2, "replicate", 1e-5, nthr=272, variant=4)
+    assert orc.rel_l2(out, ref) <= 2e-5
+
+
 def test_emu_gelu_epilogue(emu):
     from math import erf
     rng = np.random.default_rng(3)
