@@ -21,6 +21,9 @@ inline int num_pairs(const FwdParams& P) { return P.C * ((P.B + 1) / 2); }
 // Runtime-plan kernel (k_dynamic.cu).
 int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
 
+// Multi-pass path through a workspace (k_strip.cu).
+int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_bytes, cudaStream_t st);
+
 // Compile-time-plan kernels (k_static.cu, one object per registry line).
 typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, int blocks, cudaStream_t st);
 struct StaticEntry {

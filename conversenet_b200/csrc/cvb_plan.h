@@ -32,26 +32,73 @@ inline bool search(int n, int max_r, std::vector<int>& cur, std::vector<int>& be
   return any;
 }
 
-inline bool make_plan(int n, Plan1D& pl) {
+constexpr int kMaxBigPrime = 127;  // largest prime handled by the direct out-of-place butterfly
+
+// Radices of n: prime factors above the register butterflies (each its own stage, only
+// usable on the multi-pass path), then the fewest-stage factorisation of the rest.
+inline bool make_plan(int n, Plan1D& pl, bool* has_big = nullptr) {
   memset(&pl, 0, sizeof(pl));
-  if (n < 1) return false;
+  if (has_big) *has_big = false;
+  if (n < 2) return false;
   pl.n = n;
-  if (n == 1) {
-    pl.nst = 1; pl.radix[0] = 1; pl.L[0] = 1; pl.M[0] = 1;
-    return false;  // a 1-wide axis is not a useful image; reject
+  std::vector<int> radices;
+  int rest = n;
+  for (int f = 29; f <= kMaxBigPrime && f <= rest; f += 2) {
+    bool prime = true;
+    for (int d = 3; d * d <= f; d += 2) if (f % d == 0) { prime = false; break; }
+    if (!prime) continue;
+    while (rest % f == 0) { radices.insert(radices.begin(), f); rest /= f; }
   }
-  std::vector<int> cur, best;
-  search(n, 1 << 30, cur, best);
-  if (best.empty() || (int)best.size() > kMaxStages) return false;
-  pl.nst = (int)best.size();
+  if (!radices.empty() && has_big) *has_big = true;
+  if (rest > 1) {
+    std::vector<int> cur, best;
+    search(rest, 1 << 30, cur, best);
+    if (best.empty()) return false;
+    radices.insert(radices.end(), best.begin(), best.end());
+  }
+  if ((int)radices.size() > kMaxStages) return false;
+  pl.nst = (int)radices.size();
   int L = n;
   for (int i = 0; i < pl.nst; ++i) {
-    pl.radix[i] = best[i];
+    pl.radix[i] = radices[i];
     pl.L[i] = L;
-    pl.M[i] = L / best[i];
-    L /= best[i];
+    pl.M[i] = L / radices[i];
+    L /= radices[i];
   }
   return true;
+}
+
+// ---- multi-pass (strip) path geometry ----
+constexpr size_t kWorkspaceTarget = 48u << 20;  // chunk workspace kept well inside the 126 MB L2
+
+struct StripGeo {
+  int cw, rh, halo_l, halo_r;
+  size_t smem_col, smem_row;  // dynamic shared memory of the column / row kernels
+  int chunk_pairs;
+  size_t ws_bytes;
+};
+
+inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs) {
+  StripGeo g;
+  const int c = k / 2;
+  g.halo_l = s > 1 ? (c + s - 1) / s : 0;
+  g.halo_r = s > 1 ? (s - 1 + k - 1 - c) / s : 0;
+  g.cw = 16;
+  g.rh = 8;
+  const int tpc = (g.cw + g.halo_l + g.halo_r) | 1;
+  g.smem_col = ((size_t)2 * h * tpc + h + (k * k + 1) / 2) * sizeof(float2);
+  while (g.smem_col > kSmemLimit && g.cw > 2) {
+    g.cw /= 2;
+    g.smem_col = ((size_t)2 * h * ((g.cw + g.halo_l + g.halo_r) | 1) + h + (k * k + 1) / 2) * sizeof(float2);
+  }
+  g.smem_row = ((size_t)2 * g.rh * (w | 1) + w) * sizeof(float2);
+  const size_t per_pair = (size_t)h * w * sizeof(float2);
+  size_t cp = kWorkspaceTarget / per_pair;
+  if (cp < 1) cp = 1;
+  if (cp > (size_t)npairs) cp = npairs;
+  g.chunk_pairs = (int)cp;
+  g.ws_bytes = cp * per_pair;
+  return g;
 }
 
 inline size_t smem_bytes_for(int h, int w, int k, int ystash = 0) {

@@ -6,6 +6,7 @@
 #include <vector>
 #include <cstdio>
 #include "../../conversenet_b200/csrc/cvb_plan.h"
+#include "../../conversenet_b200/csrc/cvb_strip.cuh"
 
 using namespace cvb;
 
@@ -60,6 +61,37 @@ int emu_converse2d_fwd(const float* x, float* out, const void* table, const floa
     } else {
       return -100;
     }
+  }
+  return 0;
+}
+
+// The multi-pass path: the three strip kernels run block by block over a host workspace.
+int emu_converse2d_strip(const float* x, float* out, const void* table, const float* weight, int B, int C,
+                         int H, int W, int k, int s, int p, int pad_mode, int fuse_gelu, int nthr) {
+  FwdParams P;
+  P.x = x; P.out = out; P.table = (const float2*)table; P.weight = weight;
+  P.B = B; P.C = C; P.H = H; P.W = W; P.k = k; P.s = s; P.p = p; P.pad_mode = pad_mode;
+  P.fuse_gelu = fuse_gelu;
+  P.h = H + 2 * p; P.w = W + 2 * p; P.pitch = P.w | 1;
+  P.skip_mask = 0; P.ystash = 0; P.status = nullptr;
+  if (!make_plan(P.h, P.py) || !make_plan(P.w, P.px)) return -3;
+  const int npairs = C * ((B + 1) / 2);
+  StripGeo g = strip_geometry(P.h, P.w, k, s, npairs);
+  if (g.chunk_pairs > 3) g.chunk_pairs = 3;  // exercise the chunk loop
+  std::vector<float2> ws((size_t)g.chunk_pairs * P.h * P.w);
+  std::vector<float2> smem((g.smem_col > g.smem_row ? g.smem_col : g.smem_row) / sizeof(float2) + 16);
+  StripParams SP;
+  SP.f = P; SP.ws = ws.data(); SP.cw = g.cw; SP.rh = g.rh; SP.halo_l = g.halo_l; SP.halo_r = g.halo_r;
+  const int ncs = (P.w + g.cw - 1) / g.cw, nrs = (P.h + g.rh - 1) / g.rh;
+  for (int p0 = 0; p0 < npairs; p0 += g.chunk_pairs) {
+    SP.pair0 = p0;
+    SP.npair = (npairs - p0) < g.chunk_pairs ? (npairs - p0) : g.chunk_pairs;
+    for (int lp = 0; lp < SP.npair; ++lp)
+      for (int st = 0; st < ncs; ++st) strip_colfwd_body<float>(SP, lp, st, smem.data(), nthr);
+    for (int lp = 0; lp < SP.npair; ++lp)
+      for (int st = 0; st < nrs; ++st) strip_rowmid_body(SP, lp, st, smem.data(), nthr);
+    for (int lp = 0; lp < SP.npair; ++lp)
+      for (int st = 0; st < ncs; ++st) strip_colinv_body<float>(SP, lp, st, smem.data(), nthr);
   }
   return 0;
 }

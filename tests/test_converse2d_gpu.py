@@ -55,6 +55,44 @@ CONFIGS = {
 }
 
 
+LARGE = {
+    # planes that take the multi-pass path (workspace): model layers of BASELINE.json configs 3-5, batch reduced
+    "dncnn_body_268": dict(B=2, C=8, H=256, W=256, k=7, s=1, p=6, mode="circular", eps=1e-5),
+    "srres_264": dict(B=2, C=6, H=256, W=256, k=5, s=1, p=4, mode="replicate", eps=1e-5),
+    "srres_up2_260": dict(B=2, C=4, H=256, W=256, k=2, s=2, p=2, mode="replicate", eps=1e-3),
+    "srres_520": dict(B=1, C=4, H=512, W=512, k=5, s=1, p=4, mode="replicate", eps=1e-5),
+    "usrnet_block_516": dict(B=1, C=4, H=512, W=512, k=3, s=1, p=2, mode="circular", eps=1e-5),
+    "usrnet_data_512": dict(B=2, C=2, H=512, W=512, k=7, s=1, p=0, mode="circular", eps=1e-3),
+    "odd_rect_prime": dict(B=3, C=3, H=83, W=55, k=3, s=3, p=2, mode="reflect", eps=1e-5),  # 87 x 59
+}
+
+
+@pytest.mark.parametrize("name", list(LARGE))
+def test_large_planes_multi_pass(name):
+    cfg = LARGE[name]
+    x, w, b = _seeded(cfg, 4)
+    out = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    ref64 = orc.converse2d_forward(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float64)
+    assert orc.rel_l2(out, ref64) <= TOL_FP32
+
+
+def test_forced_multi_pass_matches_shared_memory_path(monkeypatch):
+    cfg = CONFIGS["odd_batch"]
+    x, w, b = _seeded(cfg, 6)
+    for s in (1, 2):
+        a = _run(x, w, b, s, cfg["p"], cfg["mode"], cfg["eps"])
+        monkeypatch.setenv("CVB_FORCE_STRIP", "1")
+        d = _run(x, w, b, s, cfg["p"], cfg["mode"], cfg["eps"])
+        monkeypatch.delenv("CVB_FORCE_STRIP")
+        assert orc.rel_l2(d, a) <= 2e-6
+    xb = torch.from_numpy(x).bfloat16().float().numpy()
+    monkeypatch.setenv("CVB_FORCE_STRIP", "1")
+    d = _run(xb, w, b, 2, cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
+    monkeypatch.delenv("CVB_FORCE_STRIP")
+    a = _run(xb, w, b, 2, cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
+    assert orc.rel_l2(d, a) <= 5e-3
+
+
 def _seeded(cfg, seed=0):
     rng = np.random.default_rng(seed)
     w, b = orc.init_weight(cfg["C"], cfg["k"], rng)

@@ -26,7 +26,7 @@ def _ptr(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
 
-def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0):
+def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0, strip=False):
     B, C, H, W = x.shape
     k = w.shape[-1]
     h, wd = H + 2 * p, W + 2 * p
@@ -37,8 +37,12 @@ def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0):
     assert rc == 0
     xf = np.ascontiguousarray(x, np.float32)
     out = np.full((B, C, H * s, W * s), np.nan, np.float32)
-    rc = lib.emu_converse2d_fwd(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
-                                PAD[mode], gelu, nthr, variant)
+    if strip:
+        rc = lib.emu_converse2d_strip(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
+                                      PAD[mode], gelu, nthr)
+    else:
+        rc = lib.emu_converse2d_fwd(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
+                                    PAD[mode], gelu, nthr, variant)
     assert rc == 0, rc
     return out
 
@@ -78,6 +82,29 @@ def test_emu_persistent_body(emu, B, s):
     ref = orc.converse2d_forward(x, w, b, s, 2, "replicate", 1e-5, dtype=np.float64)
     out = emu_forward(emu, x, w, b, s, 2, "replicate", 1e-5, nthr=272, variant=4)
     assert orc.rel_l2(out, ref) <= 2e-5
+
+
+@pytest.mark.parametrize("i", [0, 3, 5, 8, 11, 12, 13, 15, 16, 17])
+def test_emu_strip_path_golden(emu, golden, i):
+    # the multi-pass (workspace) path on the golden cases
+    c, x, w, b, ref32, ref64 = golden.case(i)
+    out = emu_forward(emu, x, w, b, c["s"], c["p"], c["mode"], c["eps"], nthr=64, strip=True)
+    assert np.isfinite(out).all()
+    assert orc.rel_l2(out, ref64) <= 2e-5
+
+
+@pytest.mark.parametrize("shape,k,s,p,mode", [
+    ((2, 2, 54, 82), 5, 1, 2, "circular"),    # 58 x 86 = (29*2) x (43*2): direct large-prime butterflies
+    ((3, 1, 25, 33), 3, 2, 2, "replicate"),   # 29 x 37: prime lengths, upsampling epilogue with halo
+    ((1, 2, 63, 30), 7, 1, 2, "reflect"),     # 67 x 34
+])
+def test_emu_strip_path_large_primes(emu, shape, k, s, p, mode):
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal(shape).astype(np.float32)
+    w, b = orc.init_weight(shape[1], k, rng)
+    ref = orc.converse2d_forward(x, w, b, s, p, mode, 1e-5, dtype=np.float64)
+    out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=96, strip=True)
+    assert orc.rel_l2(out, ref) <= 3e-5
 
 
 def test_emu_gelu_epilogue(emu):
