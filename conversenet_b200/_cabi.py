@@ -26,6 +26,8 @@ SIGNATURES = {
     "cvb_converse2d_workspace_bytes": (_c.c_size_t, [_c.c_int] * 7),
     "cvb_converse2d_fwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p] + [_c.c_int] * 10 +
                            [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "cvb_converse2d_fwd_static_scratch": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p] +
+                                          [_c.c_int] * 10 + [_c.c_void_p]),
     "cvb_plan_radices": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int), _c.c_int]),
     "cvb_fits_shared": (_c.c_int, [_c.c_int, _c.c_int]),
 }

@@ -23,6 +23,8 @@ int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t s
 
 // Multi-pass path through a workspace (k_strip.cu).
 int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_bytes, cudaStream_t st);
+// Same kernels, workspace = the library's own fixed device array (no allocation anywhere).
+int launch_strip_static_scratch(const FwdParams& P, int io_dtype, cudaStream_t st);
 
 // Compile-time-plan kernels (k_static.cu, one object per registry line).
 typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, int blocks, cudaStream_t st);

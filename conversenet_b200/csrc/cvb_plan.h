@@ -78,7 +78,8 @@ struct StripGeo {
   size_t ws_bytes;
 };
 
-inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs) {
+inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs, size_t ws_cap = kWorkspaceTarget,
+                               bool at_least_one = true) {
   StripGeo g;
   const int c = k / 2;
   g.halo_l = s > 1 ? (c + s - 1) / s : 0;
@@ -93,8 +94,8 @@ inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs) {
   }
   g.smem_row = ((size_t)2 * g.rh * (w | 1) + w) * sizeof(float2);
   const size_t per_pair = (size_t)h * w * sizeof(float2);
-  size_t cp = kWorkspaceTarget / per_pair;
-  if (cp < 1) cp = 1;
+  size_t cp = ws_cap / per_pair;
+  if (cp < 1 && at_least_one) cp = 1;  // otherwise chunk_pairs == 0: one pair does not fit the cap
   if (cp > (size_t)npairs) cp = npairs;
   g.chunk_pairs = (int)cp;
   g.ws_bytes = cp * per_pair;

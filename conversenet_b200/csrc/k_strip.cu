@@ -26,9 +26,11 @@ __global__ void __launch_bounds__(kStripThreads, 2) strip_colinv_kernel(const St
 
 namespace {
 template <typename IO>
-int launch_t(const FwdParams& P, void* workspace, size_t ws_bytes, cudaStream_t st) {
+int launch_t(const FwdParams& P, void* workspace, size_t ws_bytes, cudaStream_t st,
+             size_t ws_cap = kWorkspaceTarget, bool at_least_one = true) {
   const int npairs = num_pairs(P);
-  const StripGeo g = strip_geometry(P.h, P.w, P.k, P.s, npairs);
+  const StripGeo g = strip_geometry(P.h, P.w, P.k, P.s, npairs, ws_cap, at_least_one);
+  if (g.chunk_pairs < 1) return CVB_ERR_TOO_LARGE;
   if (!workspace || ws_bytes < g.ws_bytes) return CVB_ERR_WORKSPACE;
   if (g.smem_col > kSmemLimit || g.smem_row > kSmemLimit) return CVB_ERR_UNSUPPORTED_SIZE;
   CVB_CUDA(cudaFuncSetAttribute(strip_colfwd_kernel<IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem_col));
@@ -50,6 +52,43 @@ int launch_t(const FwdParams& P, void* workspace, size_t ws_bytes, cudaStream_t 
   return CVB_OK;
 }
 }  // namespace
+
+// ---- scratch that nobody has to allocate -------------------------------------------
+// Some callers of this library cannot call cudaMalloc (or any allocator) at the point
+// where they run the operator: code inside a stream-ordered region whose memory pool is
+// frozen, a plug-in that was handed only its input and output buffers, a latency-critical
+// loop that must not touch the allocator lock.  For them the workspace of the multi-pass
+// path lives here, in the library image: every GPU that loads the library holds these
+// CVB_STATIC_SCRATCH_BYTES until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the runtime, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[CVB_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out) {
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  CVB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return CVB_ERR_BAD_ARGUMENT;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    CVB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return CVB_OK;
+}
+
+int launch_strip_static_scratch(const FwdParams& P, int io_dtype, cudaStream_t st) {
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != CVB_OK) return rc;
+  // the chunk of plane pairs is sized to the fixed array; a plane pair that does not fit is refused
+  return io_dtype == CVB_F32
+             ? launch_t<float>(P, scratch, CVB_STATIC_SCRATCH_BYTES, st, CVB_STATIC_SCRATCH_BYTES, false)
+             : launch_t<__nv_bfloat16>(P, scratch, CVB_STATIC_SCRATCH_BYTES, st, CVB_STATIC_SCRATCH_BYTES, false);
+}
 
 int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_bytes, cudaStream_t st) {
   return io_dtype == CVB_F32 ? launch_t<float>(P, workspace, ws_bytes, st)

@@ -104,6 +104,31 @@ int cvb_converse2d_fwd(const void* x, void* out, const void* table, const float*
                        int fuse_gelu, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Converse2D forward for callers that cannot allocate device memory.
+ *
+ * Same arguments, result and error codes as cvb_converse2d_fwd, minus the workspace:
+ * the multi-pass kernels run with their scratch in a fixed array inside the library
+ * (CVB_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until the process
+ * ends).  Meant for code that runs where an allocator call is impossible or unwelcome:
+ * a plug-in that owns nothing but its input and output buffers, a region whose memory
+ * pool must not change, a real-time loop that may not take the allocator lock.  The
+ * function calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Limit: one padded plane pair, 8*(H+2p)*(W+2p) bytes, must fit the array
+ *     (about 1440 x 1440); larger planes return CVB_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (a runtime
+ *     query, no allocation); make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents.  Nothing
+ *     in it has to start at zero (every element is written before it is read), but two
+ *     calls that overlap on the GPU -- different streams, or different host threads --
+ *     race on it: serialise them.
+ * No counterpart in the reference (its op lets ATen allocate every temporary).
+ */
+#define CVB_STATIC_SCRATCH_BYTES (16u << 20)
+int cvb_converse2d_fwd_static_scratch(const void* x, void* out, const void* table, const float* weight,
+                                      int B, int C, int H, int W, int k, int s, int p, int pad_mode,
+                                      int io_dtype, int fuse_gelu, void* stream);
+
+/*
  * Describe the FFT plan chosen for a padded length n: writes up to max_stages
  * radices, returns the stage count, 0 if n is unsupported.  Host-only, no GPU.
  */
