@@ -1,0 +1,76 @@
+"""Importing this module registers `torch.ops.converse2d.forward` and
+`torch.ops.converse2d.clear_cache` with the reference's schema
+(`Converse2D/torch_converse2d/converse2d.cpp:218-227`), backed by the native library.
+
+    forward(Tensor x, Tensor x0, Tensor weight, Tensor bias, int scale, float eps=1e-5) -> Tensor
+
+`x` is the already padded plane batch (B,C,h,w), the result is the UNCROPPED
+(B,C,s*h,s*w) solve, as in the reference.  The native kernels implement the solve for
+`x0 = nearest-upsample(x)`, which is what `Converse2D.forward` passes
+(`models/util_converse.py:166`); any other `x0` is refused with a RuntimeError rather
+than answered wrongly.  Forward only.
+
+Do not import this module in a process that also loads the reference's own extension:
+a schema can be defined once.
+"""
+from collections import OrderedDict
+
+import torch
+import torch.nn.functional as F
+
+from . import functional as CF
+
+_CACHE_SLOTS = 64  # as the reference's FB cache (`converse2d.cpp:52`)
+_cache = OrderedDict()
+
+_lib = torch.library.Library("converse2d", "DEF")
+_lib.define("forward(Tensor x, Tensor x0, Tensor weight, Tensor bias, int scale, float eps=1e-5) -> Tensor")
+_lib.define("clear_cache() -> ()")
+
+
+def _forward(x, x0, weight, bias, scale, eps=1e-5):
+    if x.dim() != 4:
+        raise RuntimeError("x must be (B,C,H,W)")
+    if x0.dim() != 4:
+        raise RuntimeError("x0 must be (B,C,Hs,Ws)")
+    if weight.dim() != 4 or weight.size(0) != 1:
+        raise RuntimeError("weight must be (1,C,kh,kw)")
+    if bias.dim() != 4 or bias.size(0) != 1 or bias.size(2) != 1 or bias.size(3) != 1:
+        raise RuntimeError("bias must be (1,C,1,1)")
+    if not (x.device == x0.device == weight.device == bias.device):
+        raise RuntimeError("tensors on same device")
+    if scale < 1:
+        raise RuntimeError("scale must be >= 1")
+    if not x.is_cuda:
+        raise RuntimeError("converse2d.forward: this build only has the native CUDA path")
+    x = x.contiguous()
+    B, C, h, w = x.shape
+    if tuple(x0.shape) != (B, C, h * scale, w * scale):
+        raise RuntimeError("x0 must be (B,C,scale*H,scale*W)")
+    same = x0.data_ptr() == x.data_ptr() if scale == 1 else False
+    if not same:
+        ref = x if scale == 1 else F.interpolate(x, scale_factor=scale, mode="nearest")
+        if not torch.equal(x0, ref):
+            raise RuntimeError("converse2d.forward: only x0 = nearest-upsample(x) is implemented natively")
+    key = (x.device, weight.data_ptr(), weight._version, bias.data_ptr(), bias._version, C, h, w, int(scale),
+           float(eps))
+    hit = _cache.get(key)
+    if hit is None:
+        hit = CF.build_transfer(weight, bias, int(scale), float(eps), h, w)
+        _cache[key] = hit
+        while len(_cache) > _CACHE_SLOTS:
+            _cache.popitem(last=False)
+    else:
+        _cache.move_to_end(key)
+    table, wf = hit
+    # padding 0: the solve on the plane as given, nothing cropped
+    return CF.converse2d_forward(x, table, wf, weight.size(2), int(scale), 0, "circular")
+
+
+def _clear_cache():
+    _cache.clear()
+
+
+_lib.impl("forward", _forward, "CUDA")
+_lib.impl("forward", _forward, "CPU")  # raises: no CPU path
+_lib.impl("clear_cache", _clear_cache, "CompositeExplicitAutograd")

@@ -201,3 +201,21 @@ def test_error_behaviour_on_device():
         m(torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float16))  # unsupported dtype
     with pytest.raises(RuntimeError):
         m(torch.zeros(1, 3, 8, 8, device="cuda"))      # channel mismatch
+
+
+def test_registered_torch_op_matches_reference_contract(golden):
+    # torch.ops.converse2d.forward: padded input in, uncropped plane out (converse2d.cpp:165-209)
+    import conversenet_b200.torch_converse2d  # noqa: F401  (registers the op)
+    import torch.nn.functional as F
+    c, x, w, b, ref32, ref64 = golden.case(9)
+    p, s = c["p"], c["s"]
+    y = F.pad(torch.from_numpy(x).cuda(), [p, p, p, p], mode="circular")
+    x0 = y if s == 1 else F.interpolate(y, scale_factor=s, mode="nearest")
+    out = torch.ops.converse2d.forward(y, x0, torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda(), s, c["eps"])
+    assert tuple(out.shape) == (y.shape[0], y.shape[1], y.shape[2] * s, y.shape[3] * s)
+    crop = out[..., p * s:-p * s, p * s:-p * s].cpu().numpy()
+    assert orc.rel_l2(crop, ref64) <= TOL_FP32
+    torch.ops.converse2d.clear_cache()
+    with pytest.raises(RuntimeError):
+        torch.ops.converse2d.forward(y, torch.randn_like(x0), torch.from_numpy(w).cuda(),
+                                     torch.from_numpy(b).cuda(), s, c["eps"])

@@ -1,0 +1,86 @@
+"""Whole networks (this repo's mirrors on the GPU) against outputs of the unmodified reference.
+
+The fixtures hold the reference's fp32 and fp64 outputs on seeded inputs
+(tests/golden/make_model_golden.py); parameters are re-created from the same seed and
+checked by a checksum.  At random init the reference's own fp32 run drifts 0.5-2.3e-4
+from its fp64 run, so the bar is: ours-vs-fp64 <= max(1e-4, that drift)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import converse2d_oracle as orc
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def fx():
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return np.load(os.path.join(ROOT, "tests", "golden", "model_ref_cases.npz"))
+
+
+def _checksum(m):
+    return float(sum(p.detach().double().abs().sum() for p in m.parameters()))
+
+
+def _seed_alphas(model, seed):
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("alpha1") or n.endswith("alpha2"):
+                p.copy_(0.1 * torch.randn(p.shape, generator=g))
+            elif n.endswith("d.alpha"):
+                p.copy_(9.0 + torch.randn(p.shape, generator=g))
+
+
+def _check(out, ref32, ref64):
+    drift = orc.rel_l2(ref32, ref64)
+    assert out.shape == ref64.shape
+    assert orc.rel_l2(out, ref64) <= max(1e-4, drift)
+    assert orc.rel_l2(out, ref32) <= max(2e-4, 2 * drift)
+
+
+def test_converse_dncnn(fx):
+    from conversenet_b200.models import ConverseDnCNN
+    torch.manual_seed(101)
+    m = ConverseDnCNN().eval()
+    assert abs(_checksum(m) - float(fx["dncnn_sum"])) <= 1e-6 * float(fx["dncnn_sum"])
+    with torch.no_grad():
+        out = m.cuda()(torch.from_numpy(fx["dncnn_x"]).cuda()).cpu().numpy()
+    _check(out, fx["dncnn_ref32"], fx["dncnn_ref64"])
+
+
+def test_converse_srresnet(fx):
+    from conversenet_b200.models import ConverseMSRResNet
+    torch.manual_seed(102)
+    m = ConverseMSRResNet().eval()
+    assert abs(_checksum(m) - float(fx["srres_sum"])) <= 1e-6 * float(fx["srres_sum"])
+    with torch.no_grad():
+        out = m.cuda()(torch.from_numpy(fx["srres_x"]).cuda()).cpu().numpy()
+    _check(out, fx["srres_ref32"], fx["srres_ref64"])
+
+
+@pytest.mark.parametrize("sf", [1, 2])
+def test_converse_usrnet(fx, sf):
+    from conversenet_b200.models import ConverseUSRNet
+    torch.manual_seed(103)
+    m = ConverseUSRNet().eval()
+    _seed_alphas(m, 5)
+    assert abs(_checksum(m) - float(fx["usr_sum"])) <= 1e-6 * float(fx["usr_sum"])
+    with torch.no_grad():
+        out = m.cuda()(torch.from_numpy(fx[f"usr{sf}_x"]).cuda(), torch.from_numpy(fx["usr_k"]).cuda(), sf)
+    _check(out.cpu().numpy(), fx[f"usr{sf}_ref32"], fx[f"usr{sf}_ref64"])
+
+
+def test_conversenet_blind(fx):
+    from conversenet_b200.models import ConverseNet
+    torch.manual_seed(104)
+    m = ConverseNet().eval()
+    assert abs(_checksum(m) - float(fx["cnet_sum"])) <= 1e-6 * float(fx["cnet_sum"])
+    with torch.no_grad():
+        out = m.cuda()(torch.from_numpy(fx["cnet_x"]).cuda()).cpu().numpy()
+    _check(out, fx["cnet_ref32"], fx["cnet_ref64"])
