@@ -26,6 +26,14 @@ int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_by
 // Same kernels, workspace = the library's own fixed device array (no allocation anywhere).
 int launch_strip_static_scratch(const FwdParams& P, int io_dtype, cudaStream_t st);
 
+// Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
+struct StripParams;
+typedef int (*Strip2Launcher)(const StripParams& SP, int io_dtype, cudaStream_t st);
+struct Strip2Entry {
+  int r0, r1, s0, s1;  // axis length r0 * r1; Rader sub-plan s0 * s1 of r0 - 1 (0, 0 if r0 is a register radix)
+  Strip2Launcher A, B, C;
+};
+
 // Compile-time-plan kernels (k_static.cu, one object per registry line).
 typedef int (*StaticLauncher)(const FwdParams& P, int io_dtype, size_t smem, int blocks, cudaStream_t st);
 struct StaticEntry {

@@ -66,6 +66,9 @@ struct PassArgs {
   int N, L, M, tws;    // transform length, stage sub-length, L/R, twiddle stride N/L
   const float2* tw;    // tw[n] = (cos, sin)(2 pi n / N)
   float inv_nlines, invM;
+  int nl1, ls2;        // nl1 > 0: lines form a 2-level grid, line -> (line % nl1) * ls + (line / nl1) * ls2
+  const float2* tab;   // PASS_MID multiplier when not the per-channel transfer table (else null)
+  int tab_es, tab_ls;  //   its strides along the transform axis / across lines
 };
 
 struct IoArgs {
@@ -78,6 +81,9 @@ struct IoArgs {
   const int* rmap;    // padded row -> source row * W, or -1 (zero)
   const int* cmap;    // padded column -> source column, or -1 (zero)
   float2* ycopy;      // padded input of both planes, same layout as the FFT plane; null if not kept
+  float2* ws;         // multi-pass workspace of this block's lines (PASS_SRC_WS / PASS_DST_WS)
+  int wes, wls;       //   its element stride along the transform axis / stride between lines
+  int xoff;           // plane column of line 0 (PASS_DST_GLOBAL of a column strip)
   int yoff;           // ycopy - plane, in float2 units
 };
 
@@ -140,7 +146,9 @@ enum {
   PASS_SRC_GLOBAL = 2,  // first column stage: read x through the pad maps
   PASS_DST_GLOBAL = 4,  // last column stage at scale 1: crop and write out
   PASS_MID = 8,         // last row stage: butterfly, transfer multiply, conjugate, butterfly
-  PASS_CONJ_OUT = 16    // negate the imaginary part on the way out
+  PASS_CONJ_OUT = 16,   // negate the imaginary part on the way out
+  PASS_SRC_WS = 32,     // read the complex elements from a global workspace (io.ws, strides wes / wls)
+  PASS_DST_WS = 64      // write them to the workspace instead of shared memory
 };
 
 // CN, CL, CM, CNL: compile-time transform length, stage sub-length, L/R and line
@@ -168,7 +176,8 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
       divmod_small(t, a.M, a.invM, blk, j);
     }
     const int base = blk * aL + j;
-    float2* ptr = a.sm + line * a.ls + base * a.es;
+    const int loff = a.nl1 > 0 ? (line % a.nl1) * a.ls + (line / a.nl1) * a.ls2 : line * a.ls;
+    float2* ptr = a.sm + loff + base * a.es;
     const int st = aM * a.es;
     const int tstep = j * atws;
     float re[R], im[R];
@@ -191,6 +200,14 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
       if (io.ycopy) {  // after all loads are in flight
 #pragma unroll
         for (int q = 0; q < R; ++q) ptr[io.yoff + q * st] = make_float2(re[q], im[q]);
+      }
+    } else if (flags & PASS_SRC_WS) {
+      const float2* gp = io.ws + (size_t)line * io.wls + (size_t)base * io.wes;
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        const float2 v = gp[(size_t)(q * aM) * io.wes];
+        re[q] = v.x;
+        im[q] = v.y;
       }
     } else {
 #pragma unroll
@@ -216,10 +233,12 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
       Radix<R>::fwd(re, im);
       if ((flags & PASS_MID) && rep == 0) {
         // multiply by the transfer table and conjugate: the inverse runs on conj(spectrum)
-        const float2* tp = io.tab + (size_t)(t * R) * io.h + line;
+        const int tes = a.tab ? a.tab_es : io.h;
+        const float2* tp = a.tab ? a.tab + (t * R) * a.tab_es + line * a.tab_ls
+                                 : io.tab + (size_t)(t * R) * io.h + line;
 #pragma unroll
         for (int p = 0; p < R; ++p) {
-          const float2 g = tp[(size_t)p * io.h];
+          const float2 g = tp[(size_t)p * tes];
           const float xr = re[p], xi = im[p];
           re[p] = fmaf(-xi, g.y, xr * g.x);
           im[p] = -fmaf(xr, g.y, xi * g.x);
@@ -239,7 +258,7 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
 
     if (flags & PASS_DST_GLOBAL) {
       // crop and write both planes (column `line`, rows base + q*M)
-      const int ox = line - io.p;
+      const int ox = line + io.xoff - io.p;
       if (ox >= 0 && ox < io.W) {
 #pragma unroll
         for (int q = 0; q < R; ++q) {
@@ -253,6 +272,10 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
           }
         }
       }
+    } else if (flags & PASS_DST_WS) {
+      float2* gp = io.ws + (size_t)line * io.wls + (size_t)base * io.wes;
+#pragma unroll
+      for (int q = 0; q < R; ++q) gp[(size_t)(q * aM) * io.wes] = make_float2(re[q], osign * im[q]);
     } else {
 #pragma unroll
       for (int q = 0; q < R; ++q) ptr[q * st] = make_float2(re[q], osign * im[q]);
@@ -285,6 +308,8 @@ CVB_HD PassArgs make_pass(float2* sm, bool along_y, int pitch, int h, int w, int
   a.tw = tw;
   a.inv_nlines = 1.0f / (float)a.nlines;
   a.invM = 1.0f / (float)M;
+  a.nl1 = 0; a.ls2 = 0;
+  a.tab = nullptr; a.tab_es = 0; a.tab_ls = 0;
   return a;
 }
 
@@ -618,6 +643,10 @@ CVB_HD IoArgs make_io(const FwdParams& P, int c, int pa, int pb) {
   io.cmap = nullptr;
   io.ycopy = nullptr;
   io.yoff = 0;
+  io.ws = nullptr;
+  io.wes = 0;
+  io.wls = 0;
+  io.xoff = 0;
   return io;
 }
 
@@ -880,6 +909,16 @@ __host__ __device__ void smem_persistent_static(const FwdParams& P, unsigned cha
 }
 
 // ---------------------------------------------------------------- transfer table
+// Rader's algorithm for a large prime R that is the first stage of an axis plan (used by
+// the multi-pass kernels): tables of one axis, stored in the transfer blob behind the twiddles
+// as [bhat: R-1 float2][twiddles of R-1: R-1 float2][g^q mod R: R-1 int][g^-m mod R: R-1 int].
+struct RaderInfo {
+  int R;        // 0 = not used on this axis
+  int g;        // primitive root of R
+  Plan1D sub;   // plan of length R-1
+  int off;      // float2 offset of this axis' tables from the end of the twiddles
+};
+
 struct TransferParams {
   const float* weight;  // (C,k,k)
   const float* bias;    // (C)
@@ -887,6 +926,7 @@ struct TransferParams {
   int C, k, s, h, w;
   float eps;
   Plan1D py, px;
+  RaderInfo ry, rx;
 };
 
 // One table entry: position (posx, posy) of channel c.  fp64 throughout.
@@ -961,6 +1001,36 @@ __host__ __device__ inline void twiddle_entry(const TransferParams& T, int i) {
   const int n = i < T.h ? i : i - T.h;
   const double th = 2.0 * M_PI * (double)n / (double)N;
   tw[i] = make_float2((float)cos(th), (float)sin(th));
+}
+
+__host__ __device__ inline void rader_entry(const TransferParams& T, const RaderInfo& rb, int i) {
+  const int R = rb.R, n = R - 1;
+  float2* base = T.table + (size_t)T.C * T.h * T.w + T.h + T.w + rb.off;
+  int* perm_in = (int*)(base + 2 * n);
+  int* perm_out = perm_in + n;
+  long long gp = 1;
+  for (int e = 0; e < i; ++e) gp = gp * rb.g % R;
+  perm_in[i] = (int)gp;                       // g^i
+  long long ginv = 1;
+  for (int e = 0; e < n - 1; ++e) ginv = ginv * rb.g % R;  // g^(n-1) = g^-1
+  long long gm = 1;
+  for (int e = 0; e < i; ++e) gm = gm * ginv % R;
+  perm_out[i] = (int)gm;                      // g^-i
+  const double th = 2.0 * M_PI * (double)i / (double)n;
+  base[n + i] = make_float2((float)cos(th), (float)sin(th));
+  // bhat at digit-reversed position i: (1/n) sum_q b_q exp(-2 pi i q f / n), b_q = exp(-2 pi i g^-q / R)
+  const int f = pos_to_freq(rb.sub, i);
+  double sr = 0.0, si = 0.0;
+  long long e = 1;
+  for (int q = 0; q < n; ++q) {
+    const double a1 = -2.0 * M_PI * (double)e / (double)R;
+    const double a2 = -2.0 * M_PI * (double)(((long long)q * f) % n) / (double)n;
+    const double br = cos(a1), bi = sin(a1), cr = cos(a2), ci = sin(a2);
+    sr += br * cr - bi * ci;
+    si += br * ci + bi * cr;
+    e = e * ginv % R;
+  }
+  base[i] = make_float2((float)(sr / n), (float)(si / n));
 }
 
 }  // namespace cvb

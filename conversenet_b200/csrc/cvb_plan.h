@@ -68,6 +68,45 @@ inline bool make_plan(int n, Plan1D& pl, bool* has_big = nullptr) {
   return true;
 }
 
+// ---- Rader tables for a large prime in the first stage of an axis plan ----
+inline int primitive_root(int R) {
+  std::vector<int> fac;
+  int m = R - 1;
+  for (int f = 2; f * f <= m; ++f)
+    if (m % f == 0) { fac.push_back(f); while (m % f == 0) m /= f; }
+  if (m > 1) fac.push_back(m);
+  for (int g = 2; g < R; ++g) {
+    bool ok = true;
+    for (int f : fac) {
+      long long r = 1, b = g; int e = (R - 1) / f;
+      while (e) { if (e & 1) r = r * b % R; b = b * b % R; e >>= 1; }
+      if (r == 1) { ok = false; break; }
+    }
+    if (ok) return g;
+  }
+  return 0;
+}
+
+// Rader applies when the first stage is a large prime R and R-1 factors into register radices.
+inline RaderInfo rader_for(const Plan1D& pl, int off) {
+  RaderInfo r;
+  memset(&r, 0, sizeof(r));
+  r.off = off;
+  if (pl.nst < 1 || pl.radix[0] <= 26) return r;
+  bool big = false;
+  if (!make_plan(pl.radix[0] - 1, r.sub, &big) || big) return r;
+  r.g = primitive_root(pl.radix[0]);
+  if (r.g) r.R = pl.radix[0];
+  return r;
+}
+// float2 slots one axis' tables take in the blob: bhat, twiddles, two int permutations
+inline int rader_blob_float2(const RaderInfo& r) { return r.R ? 3 * (r.R - 1) : 0; }
+// both axes: column tables first, then row tables
+inline void rader_both(const Plan1D& py, const Plan1D& px, RaderInfo& ry, RaderInfo& rx) {
+  ry = rader_for(py, 0);
+  rx = rader_for(px, rader_blob_float2(ry));
+}
+
 // ---- multi-pass (strip) path geometry ----
 constexpr size_t kWorkspaceTarget = 48u << 20;  // chunk workspace kept well inside the 126 MB L2
 
@@ -78,21 +117,44 @@ struct StripGeo {
   size_t ws_bytes;
 };
 
+inline bool plan_has_big(const Plan1D& pl) {
+  for (int i = 0; i < pl.nst; ++i)
+    if (pl.radix[i] > 26) return true;
+  return false;
+}
+
+// Shared memory of a column-strip block: one tile (two when a large prime needs the
+// out-of-place butterfly), the column twiddles, the taps.
+inline size_t strip_smem_col(int h, int cw, int halo, int k, bool big) {
+  return ((size_t)(big ? 2 : 1) * h * ((cw + halo) | 1) + h + (big ? 3 * kMaxBigPrime : 0) + (k * k + 1) / 2) *
+         sizeof(float2);
+}
+inline size_t strip_smem_row(int w, int rh, bool big) {
+  return ((size_t)(big ? 2 : 1) * rh * (w | 1) + w + (big ? 3 * kMaxBigPrime : 0)) * sizeof(float2);
+}
+
 inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs, size_t ws_cap = kWorkspaceTarget,
                                bool at_least_one = true) {
   StripGeo g;
   const int c = k / 2;
   g.halo_l = s > 1 ? (c + s - 1) / s : 0;
   g.halo_r = s > 1 ? (s - 1 + k - 1 - c) / s : 0;
-  g.cw = 16;
-  g.rh = 8;
-  const int tpc = (g.cw + g.halo_l + g.halo_r) | 1;
-  g.smem_col = ((size_t)2 * h * tpc + h + (k * k + 1) / 2) * sizeof(float2);
-  while (g.smem_col > kSmemLimit && g.cw > 2) {
-    g.cw /= 2;
-    g.smem_col = ((size_t)2 * h * ((g.cw + g.halo_l + g.halo_r) | 1) + h + (k * k + 1) / 2) * sizeof(float2);
-  }
-  g.smem_row = ((size_t)2 * g.rh * (w | 1) + w) * sizeof(float2);
+  Plan1D py, px;
+  const bool bigy = make_plan(h, py) && plan_has_big(py);
+  const bool bigx = make_plan(w, px) && plan_has_big(px);
+  // widest strip that still lets three blocks share an SM, else the widest that fits at all
+  const size_t want = kSmemLimit / 3;
+  g.cw = 2;
+  for (int cw : {32, 16, 8, 4, 2})
+    if (strip_smem_col(h, cw, g.halo_l + g.halo_r, k, bigy) <= want) { g.cw = cw; break; }
+  if (strip_smem_col(h, g.cw, g.halo_l + g.halo_r, k, bigy) > want)
+    for (int cw : {16, 8, 4, 2})
+      if (strip_smem_col(h, cw, g.halo_l + g.halo_r, k, bigy) <= kSmemLimit) { g.cw = cw; break; }
+  g.rh = 1;
+  for (int rh : {32, 16, 8, 4, 2, 1})
+    if (strip_smem_row(w, rh, bigx) <= want) { g.rh = rh; break; }
+  g.smem_col = strip_smem_col(h, g.cw, g.halo_l + g.halo_r, k, bigy);
+  g.smem_row = strip_smem_row(w, g.rh, bigx);
   const size_t per_pair = (size_t)h * w * sizeof(float2);
   size_t cp = ws_cap / per_pair;
   if (cp < 1 && at_least_one) cp = 1;  // otherwise chunk_pairs == 0: one pair does not fit the cap

@@ -31,6 +31,8 @@ struct StripParams {
   int cw;           // columns per column strip
   int rh;           // rows per row strip
   int halo_l, halo_r;  // extra columns the epilogue reads left / right of a strip (s > 1)
+  int big_y, big_x;    // the column / row plan has a large-prime stage (second tile buffer present)
+  RaderInfo ry, rx;
 };
 
 // ---- direct butterfly for a large prime radix, out of place (src -> dst) ----
@@ -119,20 +121,131 @@ CVB_HD void twiddle_sweep(int tid, int nthr, float2* buf, const PassArgs& a, int
 }
 
 
+// ---- Rader stage: shared-memory tables of one axis ----
+struct RaderSmem {
+  const float2* bhat;   // FFT of the fixed sequence, digit-reversed, scaled by 1/(R-1)
+  const float2* tw;     // twiddles of length R-1
+  const int* perm_in;   // g^q mod R
+  const int* perm_out;  // g^-m mod R
+};
+CVB_HD int rader_floats2(int R) { return 3 * (R - 1); }  // bhat, tw, two int tables (= one float2 table)
+CVB_HD RaderSmem rader_views(const float2* base, int R) {
+  RaderSmem r;
+  r.bhat = base;
+  r.tw = base + (R - 1);
+  r.perm_in = (const int*)(base + 2 * (R - 1));
+  r.perm_out = r.perm_in + (R - 1);
+  return r;
+}
+
+// gather: oth[p = q+1] = x[g^q] (pre-twiddled by W_N^(j p) for an inverse-type stage), oth[0] = x[0]
+CVB_HD void rader_gather(int tid, int nthr, const float2* cur, float2* oth, const PassArgs& a, int R,
+                         const RaderSmem& rs, bool pre) {
+  const int total = a.nlines * a.M * R;
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int rest, line;
+    divmod_small(wi, a.nlines, inv_nl, rest, line);
+    const int q = rest / a.M, j = rest - q * a.M;  // q = 0 .. R-1; q == R-1 stands for element 0
+    const int src_p = (q == R - 1) ? 0 : rs.perm_in[q];
+    const int dst_p = (q == R - 1) ? 0 : q + 1;
+    float2 v = cur[line * a.ls + (j + src_p * a.M) * a.es];
+    if (pre && src_p != 0 && j != 0) {
+      const float2 wv = a.tw[j * src_p * a.tws];
+      v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
+    }
+    oth[line * a.ls + (j + dst_p * a.M) * a.es] = v;
+  }
+}
+
+// X_0 = sum of the (pre-twiddled) inputs, which `oth` now holds; written to its final place in cur
+CVB_HD void rader_dc(int tid, int nthr, float2* cur, const float2* oth, const PassArgs& a, int R, float osign) {
+  const int total = a.nlines * a.M;
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int j, line;
+    divmod_small(wi, a.nlines, inv_nl, j, line);
+    const float2* ip = oth + line * a.ls + j * a.es;
+    float sr = 0.f, si = 0.f;
+    for (int p = 0; p < R; ++p) {
+      const float2 v = ip[p * a.M * a.es];
+      sr += v.x; si += v.y;
+    }
+    cur[line * a.ls + j * a.es] = make_float2(sr, osign * si);
+  }
+}
+
+// scatter: X[g^-m] = x_0 + conj(c_m), post-twiddled by W_N^(j k) for a forward stage
+CVB_HD void rader_scatter(int tid, int nthr, float2* cur, const float2* oth, const PassArgs& a, int R,
+                          const RaderSmem& rs, bool post, float osign) {
+  const int total = a.nlines * a.M * (R - 1);
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int rest, line;
+    divmod_small(wi, a.nlines, inv_nl, rest, line);
+    const int m = rest / a.M, j = rest - m * a.M;
+    const float2* ip = oth + line * a.ls + j * a.es;
+    const float2 x0 = ip[0];
+    const float2 c = ip[(m + 1) * a.M * a.es];
+    float vr = x0.x + c.x, vi = x0.y - c.y;
+    const int k = rs.perm_out[m];
+    if (post && j != 0) {
+      const float2 wv = a.tw[j * k * a.tws];
+      const float tr = fmaf(vi, wv.y, vr * wv.x), ti = fmaf(-vr, wv.y, vi * wv.x);
+      vr = tr; vi = ti;
+    }
+    cur[line * a.ls + (j + k * a.M) * a.es] = make_float2(vr, osign * vi);
+  }
+}
+
+// PassArgs of stage `i` of the length-(R-1) sub-transform living in `oth` behind element 0
+CVB_HD PassArgs rader_sub_pass(float2* oth, const PassArgs& a, const RaderInfo& ri, int i, const RaderSmem& rs) {
+  PassArgs s = a;
+  s.sm = oth + a.M * a.es;          // element p = 1 of every sub-line
+  s.es = a.M * a.es;
+  s.nl1 = a.nlines;                 // sub-line (line, j): offset line * ls + j * (outer es)
+  s.ls2 = a.es;
+  s.nlines = a.nlines * a.M;
+  s.inv_nlines = 1.0f / (float)s.nlines;
+  s.N = ri.sub.n; s.L = ri.sub.L[i]; s.M = ri.sub.M[i]; s.tws = ri.sub.n / ri.sub.L[i];
+  s.invM = 1.0f / (float)s.M;
+  s.tw = rs.tw;
+  s.tab = rs.bhat; s.tab_es = 1; s.tab_ls = 0;
+  return s;
+}
+
 // One FFT stage on a shared-memory tile.  Register radices work in place; a large
 // prime goes src -> dst and the caller swaps the buffers.  Expands to whole phases.
-#define CVB_TILE_STAGE(pl, i, along_y_, cur, oth, tpitch, nlines_, twp, flags_)                          \
+#define CVB_TILE_STAGE(pl, i, along_y_, cur, oth, tpitch, nlines_, twp, flags_, rinfo, rsm)                \
   do {                                                                                                   \
     PassArgs a_ = make_pass(cur, along_y_, tpitch, 0, 0, (pl).n, (pl).L[i], (pl).M[i], twp);            \
     a_.nlines = (nlines_);                                                                               \
     a_.inv_nlines = 1.0f / (float)(nlines_);                                                             \
     const int R_ = (pl).radix[i];                                                                        \
+    const bool pre_ = ((flags_) & PASS_PRE) != 0;                                                        \
+    const float osg_ = ((flags_) & PASS_CONJ_OUT) ? -1.0f : 1.0f;                                        \
     if (R_ <= kMaxRegisterRadix) {                                                                       \
       CVB_PHASE((run_pass<float>(R_, tid, nthr, a_, io, (flags_))));                                     \
+    } else if ((i) == 0 && (rinfo).R == R_) {                                                            \
+      CVB_PHASE(rader_gather(tid, nthr, cur, oth, a_, R_, rsm, pre_));                                   \
+      CVB_PHASE(rader_dc(tid, nthr, cur, oth, a_, R_, osg_));                                            \
+      const int ns_ = (rinfo).sub.nst;                                                                   \
+      for (int u_ = 0; u_ + 1 < ns_; ++u_) {                                                             \
+        const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, u_, rsm);                                     \
+        CVB_PHASE((run_pass<float>((rinfo).sub.radix[u_], tid, nthr, s_, io, 0)));                       \
+      }                                                                                                  \
+      {                                                                                                  \
+        const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, ns_ - 1, rsm);                                \
+        CVB_PHASE((run_pass<float>((rinfo).sub.radix[ns_ - 1], tid, nthr, s_, io, PASS_MID)));           \
+      }                                                                                                  \
+      for (int u_ = ns_ - 2; u_ >= 0; --u_) {                                                            \
+        const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, u_, rsm);                                     \
+        CVB_PHASE((run_pass<float>((rinfo).sub.radix[u_], tid, nthr, s_, io, PASS_PRE)));                \
+      }                                                                                                  \
+      CVB_PHASE(rader_scatter(tid, nthr, cur, oth, a_, R_, rsm, !pre_, osg_));                           \
     } else {                                                                                             \
-      if ((flags_) & PASS_PRE) CVB_PHASE(twiddle_sweep(tid, nthr, cur, a_, R_));                         \
-      CVB_PHASE(bigprime_pass(tid, nthr, cur, oth, a_, R_, !((flags_) & PASS_PRE),                       \
-                              ((flags_) & PASS_CONJ_OUT) ? -1.0f : 1.0f));                               \
+      if (pre_) CVB_PHASE(twiddle_sweep(tid, nthr, cur, a_, R_));                                        \
+      CVB_PHASE(bigprime_pass(tid, nthr, cur, oth, a_, R_, !pre_, osg_));                                \
       float2* t_ = cur; cur = oth; oth = t_;                                                             \
     }                                                                                                    \
   } while (0)
@@ -151,23 +264,37 @@ CVB_HD void copy_twiddles(int tid, int nthr, float2* dst, const float2* src, int
   for (int i = tid; i < n; i += nthr) dst[i] = src[i];
 }
 
+constexpr int kTileUnroll = 8;  // independent global accesses in flight per thread in the tile copies
+
 // tile[row][col] = padded x at (row, xfirst + col) for both planes; columns wrap modulo w
 template <typename IO>
 CVB_HD void tile_load_x(int tid, int nthr, float2* tile, int tp, int nc, int xfirst, const FwdParams& P,
                         const IoArgs& io) {
   const float inv_nc = 1.0f / (float)nc;
-  for (int i = tid; i < P.h * nc; i += nthr) {
-    int row, col;
-    divmod_small(i, nc, inv_nc, row, col);
-    const int ry = pad_index(row - P.p, P.H, P.pad_mode);
-    const int cx = pad_index(xfirst + col - P.p, P.W, P.pad_mode);
-    float va = 0.f, vb = 0.f;
-    if (ry >= 0 && cx >= 0) {
-      const size_t off = (size_t)ry * P.W + cx;
-      va = ld_io<IO>(io.xa, off);
-      if (io.xb) vb = ld_io<IO>(io.xb, off);
+  const int total = P.h * nc;
+  for (int i0 = tid; i0 < total; i0 += nthr * kTileUnroll) {
+    float va[kTileUnroll], vb[kTileUnroll];
+    int dst[kTileUnroll];
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u) {
+      const int i = i0 + u * nthr;
+      va[u] = 0.f; vb[u] = 0.f; dst[u] = -1;
+      if (i < total) {
+        int row, col;
+        divmod_small(i, nc, inv_nc, row, col);
+        dst[u] = row * tp + col;
+        const int ry = pad_index(row - P.p, P.H, P.pad_mode);
+        const int cx = pad_index(xfirst + col - P.p, P.W, P.pad_mode);
+        if (ry >= 0 && cx >= 0) {
+          const size_t off = (size_t)ry * P.W + cx;
+          va[u] = ld_io<IO>(io.xa, off);
+          if (io.xb) vb[u] = ld_io<IO>(io.xb, off);
+        }
+      }
     }
-    tile[row * tp + col] = make_float2(va, vb);
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u)
+      if (dst[u] >= 0) tile[dst[u]] = make_float2(va[u], vb[u]);
   }
 }
 
@@ -175,13 +302,28 @@ CVB_HD void tile_load_x(int tid, int nthr, float2* tile, int tp, int nc, int xfi
 CVB_HD void tile_from_ws(int tid, int nthr, float2* tile, int tp, int nr, int nc, const float2* S, int w,
                          int xfirst) {
   const float inv_nc = 1.0f / (float)nc;
-  for (int i = tid; i < nr * nc; i += nthr) {
-    int row, col;
-    divmod_small(i, nc, inv_nc, row, col);
-    int x = xfirst + col;
-    if (x < 0) x += w;
-    if (x >= w) x -= w;
-    tile[row * tp + col] = S[(size_t)row * w + x];
+  const int total = nr * nc;
+  for (int i0 = tid; i0 < total; i0 += nthr * kTileUnroll) {
+    float2 v[kTileUnroll];
+    int dst[kTileUnroll];
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u) {
+      const int i = i0 + u * nthr;
+      dst[u] = -1;
+      v[u] = make_float2(0.f, 0.f);
+      if (i < total) {
+        int row, col;
+        divmod_small(i, nc, inv_nc, row, col);
+        int x = xfirst + col;
+        if (x < 0) x += w;
+        if (x >= w) x -= w;
+        dst[u] = row * tp + col;
+        v[u] = S[(size_t)row * w + x];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u)
+      if (dst[u] >= 0) tile[dst[u]] = v[u];
   }
 }
 CVB_HD void tile_to_ws(int tid, int nthr, const float2* tile, int tp, int nr, int nc, float2* S, int w,
@@ -198,13 +340,28 @@ CVB_HD void tile_to_ws(int tid, int nthr, const float2* tile, int tp, int nr, in
 CVB_HD void tile_multiply(int tid, int nthr, float2* tile, int tp, int nr, int w, int h, int y0,
                           const float2* tab) {
   const float inv_nr = 1.0f / (float)nr;
-  for (int i = tid; i < nr * w; i += nthr) {
-    int posx, r;
-    divmod_small(i, nr, inv_nr, posx, r);
-    const float2 g = tab[(size_t)posx * h + y0 + r];
-    float2* e = tile + r * tp + posx;
-    const float2 v = *e;
-    *e = make_float2(fmaf(-v.y, g.y, v.x * g.x), -fmaf(v.x, g.y, v.y * g.x));
+  const int total = nr * w;
+  for (int i0 = tid; i0 < total; i0 += nthr * kTileUnroll) {
+    float2 g[kTileUnroll];
+    int dst[kTileUnroll];
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u) {
+      const int i = i0 + u * nthr;
+      dst[u] = -1;
+      g[u] = make_float2(0.f, 0.f);
+      if (i < total) {
+        int posx, r;
+        divmod_small(i, nr, inv_nr, posx, r);
+        g[u] = tab[(size_t)posx * h + y0 + r];
+        dst[u] = r * tp + posx;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kTileUnroll; ++u) {
+      if (dst[u] < 0) continue;
+      const float2 v = tile[dst[u]];
+      tile[dst[u]] = make_float2(fmaf(-v.y, g[u].y, v.x * g[u].x), -fmaf(v.x, g[u].y, v.y * g[u].x));
+    }
   }
 }
 
@@ -217,14 +374,19 @@ __host__ __device__ void strip_colfwd_body(const StripParams& SP, int lp, int st
   const int x0 = strip * SP.cw;
   const int nc = (w - x0) < SP.cw ? (w - x0) : SP.cw;
   const int tp = SP.cw | 1;
+  const bool big = SP.big_y != 0;
   float2* cur = smem;
-  float2* oth = smem + h * tp;
+  float2* oth = big ? smem + h * tp : smem;
   float2* twy = oth + h * tp;
+  float2* rtab = twy + h;
+  const int nrt = SP.ry.R ? rader_floats2(SP.ry.R) : 0;
+  const RaderSmem rsm = rader_views(rtab, SP.ry.R ? SP.ry.R : 1);
+  const float2* blob = P.table + (size_t)P.C * h * w;
   int c;
   const IoArgs io = strip_io<IO>(P, SP.pair0 + lp, c);
-  CVB_PHASE((copy_twiddles(tid, nthr, twy, P.table + (size_t)P.C * h * w, h),
+  CVB_PHASE((copy_twiddles(tid, nthr, twy, blob, h), copy_twiddles(tid, nthr, rtab, blob + h + w + SP.ry.off, nrt),
              tile_load_x<IO>(tid, nthr, cur, tp, nc, x0, P, io)));
-  for (int i = 0; i < P.py.nst; ++i) CVB_TILE_STAGE(P.py, i, true, cur, oth, tp, nc, twy, 0);
+  for (int i = 0; i < P.py.nst; ++i) CVB_TILE_STAGE(P.py, i, true, cur, oth, tp, nc, twy, 0, SP.ry, rsm);
   CVB_PHASE(tile_to_ws(tid, nthr, cur, tp, h, nc, SP.ws + (size_t)lp * h * w, w, x0));
 }
 
@@ -237,17 +399,22 @@ __host__ __device__ inline void strip_rowmid_body(const StripParams& SP, int lp,
   const int y0 = strip * SP.rh;
   const int nr = (h - y0) < SP.rh ? (h - y0) : SP.rh;
   const int tp = w | 1;
+  const bool big = SP.big_x != 0;
   float2* cur = smem;
-  float2* oth = smem + SP.rh * tp;
+  float2* oth = big ? smem + SP.rh * tp : smem;
   float2* twx = oth + SP.rh * tp;
+  float2* rtab = twx + w;
+  const int nrt = SP.rx.R ? rader_floats2(SP.rx.R) : 0;
+  const RaderSmem rsm = rader_views(rtab, SP.rx.R ? SP.rx.R : 1);
+  const float2* blob = P.table + (size_t)P.C * h * w;
   int c;
   const IoArgs io = strip_io<float>(P, SP.pair0 + lp, c);
   float2* S = SP.ws + (size_t)lp * h * w + (size_t)y0 * w;
-  CVB_PHASE((copy_twiddles(tid, nthr, twx, P.table + (size_t)P.C * h * w + h, w),
+  CVB_PHASE((copy_twiddles(tid, nthr, twx, blob + h, w), copy_twiddles(tid, nthr, rtab, blob + h + w + SP.rx.off, nrt),
              tile_from_ws(tid, nthr, cur, tp, nr, w, S, w, 0)));
-  for (int i = 0; i < P.px.nst; ++i) CVB_TILE_STAGE(P.px, i, false, cur, oth, tp, nr, twx, 0);
+  for (int i = 0; i < P.px.nst; ++i) CVB_TILE_STAGE(P.px, i, false, cur, oth, tp, nr, twx, 0, SP.rx, rsm);
   CVB_PHASE(tile_multiply(tid, nthr, cur, tp, nr, w, h, y0, io.tab));
-  for (int i = P.px.nst - 1; i >= 0; --i) CVB_TILE_STAGE(P.px, i, false, cur, oth, tp, nr, twx, PASS_PRE);
+  for (int i = P.px.nst - 1; i >= 0; --i) CVB_TILE_STAGE(P.px, i, false, cur, oth, tp, nr, twx, PASS_PRE, SP.rx, rsm);
   CVB_PHASE(tile_to_ws(tid, nthr, cur, tp, nr, w, S, w, 0));
 }
 
@@ -326,21 +493,26 @@ __host__ __device__ void strip_colinv_body(const StripParams& SP, int lp, int st
   const int hl = P.s > 1 ? SP.halo_l : 0, hr = P.s > 1 ? SP.halo_r : 0;
   const int nt = nc + hl + hr;              // tile columns
   const int tp = (SP.cw + SP.halo_l + SP.halo_r) | 1;
+  const bool big = SP.big_y != 0;
   float2* cur = smem;
-  float2* oth = smem + h * tp;
+  float2* oth = big ? smem + h * tp : smem;
   float2* twy = oth + h * tp;
-  float* wk = (float*)(twy + h);
+  float2* rtab = twy + h;
+  const int nrt = SP.ry.R ? rader_floats2(SP.ry.R) : 0;
+  const RaderSmem rsm = rader_views(rtab, SP.ry.R ? SP.ry.R : 1);
+  const float2* blob = P.table + (size_t)P.C * h * w;
+  float* wk = (float*)(rtab + nrt);
   int c;
   const IoArgs io = strip_io<IO>(P, SP.pair0 + lp, c);
   const float2* S = SP.ws + (size_t)lp * h * w;
-  CVB_PHASE((copy_twiddles(tid, nthr, twy, P.table + (size_t)P.C * h * w, h),
+  CVB_PHASE((copy_twiddles(tid, nthr, twy, blob, h), copy_twiddles(tid, nthr, rtab, blob + h + w + SP.ry.off, nrt),
              tile_from_ws(tid, nthr, cur, tp, h, nt, S, w, x0 - hl)));
   if (P.s > 1) {
     const float* gw = P.weight + (size_t)c * P.k * P.k;
     CVB_PHASE(copy_floats(tid, nthr, wk, gw, P.k * P.k));
   }
   for (int i = P.py.nst - 1; i >= 0; --i)
-    CVB_TILE_STAGE(P.py, i, true, cur, oth, tp, nt, twy, PASS_PRE | (i == 0 ? PASS_CONJ_OUT : 0));
+    CVB_TILE_STAGE(P.py, i, true, cur, oth, tp, nt, twy, PASS_PRE | (i == 0 ? PASS_CONJ_OUT : 0), SP.ry, rsm);
   if (P.s == 1) {
     CVB_PHASE(tile_store_crop<IO>(tid, nthr, cur, tp, nc, x0, P, io));
   } else {

@@ -1,0 +1,63 @@
+// Multi-pass kernels with a compile-time axis plan N = R0 * R1 (Rader sub-plan S0 * S1 when
+// R0 is a large prime).  Built once per line of the axis-plan registry with
+// -DCVB_R0=.. -DCVB_R1=.. -DCVB_S0=.. -DCVB_S1=.. ; kernels A and C use the plan for the
+// column axis, kernel B for the row axis.
+#include "../../include/converse_b200.h"
+#include "cvb_internal.h"
+#include "cvb_strip2.cuh"
+
+#define CVB_CAT_(n, a, b) launch_strip2##n##_##a##_##b
+#define CVB_CAT(n, a, b) CVB_CAT_(n, a, b)
+
+namespace cvb {
+
+constexpr int kLines = strip2_lines(CVB_R0 * CVB_R1, CVB_R0);
+
+template <typename IO, int R0, int R1, int S0, int S1>
+__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_A_kernel(const StripParams SP) {
+  extern __shared__ float2 smem[];
+  strip2_A_body<IO, R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
+}
+template <int R0, int R1, int S0, int S1>
+__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_B_kernel(const StripParams SP) {
+  extern __shared__ float2 smem[];
+  strip2_B_body<R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
+}
+template <typename IO, int R0, int R1, int S0, int S1>
+__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_C_kernel(const StripParams SP) {
+  extern __shared__ float2 smem[];
+  strip2_C_body<IO, R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
+}
+
+namespace {
+template <typename K>
+int launch_k(K kernel, const StripParams& SP, int nstrips, size_t smem, cudaStream_t st) {
+  CVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kernel<<<dim3(nstrips, SP.npair), kStrip2Threads, smem, st>>>(SP);
+  CVB_CUDA(cudaGetLastError());
+  return CVB_OK;
+}
+}  // namespace
+
+int CVB_CAT(A, CVB_R0, CVB_R1)(const StripParams& SP, int io_dtype, cudaStream_t st) {
+  const size_t smem = strip2_smem(CVB_R0 * CVB_R1, kLines, CVB_R0, SP.f.k);
+  const int n = (SP.f.w + kLines - 1) / kLines;
+  return io_dtype == CVB_F32
+             ? launch_k(strip2_A_kernel<float, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, SP, n, smem, st)
+             : launch_k(strip2_A_kernel<__nv_bfloat16, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, SP, n, smem, st);
+}
+int CVB_CAT(B, CVB_R0, CVB_R1)(const StripParams& SP, int, cudaStream_t st) {
+  const size_t smem = strip2_smem(CVB_R0 * CVB_R1, kLines, CVB_R0, SP.f.k);
+  const int n = (SP.f.h + kLines - 1) / kLines;
+  return launch_k(strip2_B_kernel<CVB_R0, CVB_R1, CVB_S0, CVB_S1>, SP, n, smem, st);
+}
+int CVB_CAT(C, CVB_R0, CVB_R1)(const StripParams& SP, int io_dtype, cudaStream_t st) {
+  const size_t smem = strip2_smem(CVB_R0 * CVB_R1, kLines, CVB_R0, SP.f.k);
+  const int cw = kLines - SP.halo_l - SP.halo_r;
+  const int n = (SP.f.w + cw - 1) / cw;
+  return io_dtype == CVB_F32
+             ? launch_k(strip2_C_kernel<float, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, SP, n, smem, st)
+             : launch_k(strip2_C_kernel<__nv_bfloat16, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, SP, n, smem, st);
+}
+
+}  // namespace cvb

@@ -6,9 +6,25 @@
 #include <vector>
 #include <cstdio>
 #include "../../conversenet_b200/csrc/cvb_plan.h"
-#include "../../conversenet_b200/csrc/cvb_strip.cuh"
+#include "../../conversenet_b200/csrc/cvb_strip2.cuh"
 
 using namespace cvb;
+
+template <typename FA, typename FB, typename FC>
+static void run_strip2(StripParams& SP, int npairs, int chunk, std::vector<float2>& smem, int nthr, FA fa, FB fb,
+                       FC fc, int lny, int lnx) {
+  const FwdParams& P = SP.f;
+  const int cwc = lny - SP.halo_l - SP.halo_r;
+  const int nA = (P.w + lny - 1) / lny, nB = (P.h + lnx - 1) / lnx, nC = (P.w + cwc - 1) / cwc;
+  for (int p0 = 0; p0 < npairs; p0 += chunk) {
+    SP.pair0 = p0;
+    SP.npair = (npairs - p0) < chunk ? (npairs - p0) : chunk;
+    for (int lp = 0; lp < SP.npair; ++lp) for (int st = 0; st < nA; ++st) fa(SP, lp, st, smem.data(), nthr);
+    for (int lp = 0; lp < SP.npair; ++lp) for (int st = 0; st < nB; ++st) fb(SP, lp, st, smem.data(), nthr);
+    for (int lp = 0; lp < SP.npair; ++lp) for (int st = 0; st < nC; ++st) fc(SP, lp, st, smem.data(), nthr);
+  }
+}
+
 
 extern "C" {
 
@@ -22,6 +38,9 @@ int emu_build_transfer(const float* weight, const float* bias, int C, int k, int
     for (int px = 0; px < w; ++px)
       for (int py = 0; py < h; ++py) transfer_entry(T, c, py, px);
   for (int i = 0; i < h + w; ++i) twiddle_entry(T, i);
+  rader_both(T.py, T.px, T.ry, T.rx);
+  for (int i = 0; T.ry.R && i < T.ry.R - 1; ++i) rader_entry(T, T.ry, i);
+  for (int i = 0; T.rx.R && i < T.rx.R - 1; ++i) rader_entry(T, T.rx, i);
   return 0;
 }
 
@@ -82,6 +101,9 @@ int emu_converse2d_strip(const float* x, float* out, const void* table, const fl
   std::vector<float2> smem((g.smem_col > g.smem_row ? g.smem_col : g.smem_row) / sizeof(float2) + 16);
   StripParams SP;
   SP.f = P; SP.ws = ws.data(); SP.cw = g.cw; SP.rh = g.rh; SP.halo_l = g.halo_l; SP.halo_r = g.halo_r;
+  SP.big_y = plan_has_big(P.py) ? 1 : 0; SP.big_x = plan_has_big(P.px) ? 1 : 0;
+  rader_both(P.py, P.px, SP.ry, SP.rx);
+  if (nthr < 0) { nthr = -nthr; SP.ry.R = 0; SP.rx.R = 0; }  // negative thread count: direct large-prime butterflies
   const int ncs = (P.w + g.cw - 1) / g.cw, nrs = (P.h + g.rh - 1) / g.rh;
   for (int p0 = 0; p0 < npairs; p0 += g.chunk_pairs) {
     SP.pair0 = p0;
@@ -92,6 +114,37 @@ int emu_converse2d_strip(const float* x, float* out, const void* table, const fl
       for (int st = 0; st < nrs; ++st) strip_rowmid_body(SP, lp, st, smem.data(), nthr);
     for (int lp = 0; lp < SP.npair; ++lp)
       for (int st = 0; st < ncs; ++st) strip_colinv_body<float>(SP, lp, st, smem.data(), nthr);
+  }
+  return 0;
+}
+
+// The multi-pass path with compile-time axis plans (transposed workspace), for the two plane
+// sizes instantiated here: 34 x 42 = (17*2) x (7*6) and 58 x 86 = (29*2) x (43*2) with Rader.
+int emu_converse2d_strip2(const float* x, float* out, const void* table, const float* weight, int B, int C,
+                          int H, int W, int k, int s, int p, int pad_mode, int fuse_gelu, int nthr) {
+  FwdParams P;
+  P.x = x; P.out = out; P.table = (const float2*)table; P.weight = weight;
+  P.B = B; P.C = C; P.H = H; P.W = W; P.k = k; P.s = s; P.p = p; P.pad_mode = pad_mode;
+  P.fuse_gelu = fuse_gelu;
+  P.h = H + 2 * p; P.w = W + 2 * p; P.pitch = P.w | 1;
+  P.skip_mask = 0; P.ystash = 0; P.status = nullptr;
+  if (!make_plan(P.h, P.py) || !make_plan(P.w, P.px)) return -3;
+  const int npairs = C * ((B + 1) / 2);
+  StripGeo g = strip_geometry(P.h, P.w, k, s, npairs);
+  std::vector<float2> ws((size_t)2 * P.h * P.w);
+  std::vector<float2> smem(strip2_smem(128, 32, 127, k) / sizeof(float2) + 64);
+  StripParams SP;
+  SP.f = P; SP.ws = ws.data(); SP.cw = g.cw; SP.rh = g.rh; SP.halo_l = g.halo_l; SP.halo_r = g.halo_r;
+  SP.big_y = plan_has_big(P.py) ? 1 : 0; SP.big_x = plan_has_big(P.px) ? 1 : 0;
+  rader_both(P.py, P.px, SP.ry, SP.rx);
+  if (P.h == 34 && P.w == 42) {
+    run_strip2(SP, npairs, 2, smem, nthr, strip2_A_body<float, 17, 2, 0, 0>, strip2_B_body<7, 6, 0, 0>,
+               strip2_C_body<float, 17, 2, 0, 0>, strip2_lines(34, 17), strip2_lines(42, 7));
+  } else if (P.h == 58 && P.w == 86) {
+    run_strip2(SP, npairs, 2, smem, nthr, strip2_A_body<float, 29, 2, 7, 4>, strip2_B_body<43, 2, 7, 6>,
+               strip2_C_body<float, 29, 2, 7, 4>, strip2_lines(58, 29), strip2_lines(86, 43));
+  } else {
+    return -100;
   }
   return 0;
 }

@@ -26,18 +26,21 @@ def _ptr(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
 
-def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0, strip=False):
+def emu_forward(lib, x, w, b, s, p, mode, eps, gelu=0, nthr=96, variant=0, strip=False, strip2=False):
     B, C, H, W = x.shape
     k = w.shape[-1]
     h, wd = H + 2 * p, W + 2 * p
-    table = np.zeros((C * h * wd + h + wd, 2), np.float32)
+    table = np.zeros((C * h * wd + h + wd + 6 * 128, 2), np.float32)  # room for the large-prime tables
     wf = np.ascontiguousarray(w.reshape(C, k, k), np.float32)
     bf = np.ascontiguousarray(b.reshape(C), np.float32)
     rc = lib.emu_build_transfer(_ptr(wf), _ptr(bf), C, k, s, h, wd, ctypes.c_float(eps), _ptr(table))
     assert rc == 0
     xf = np.ascontiguousarray(x, np.float32)
     out = np.full((B, C, H * s, W * s), np.nan, np.float32)
-    if strip:
+    if strip2:
+        rc = lib.emu_converse2d_strip2(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
+                                       PAD[mode], gelu, nthr)
+    elif strip:
         rc = lib.emu_converse2d_strip(_ptr(xf), _ptr(out), _ptr(table), _ptr(wf), B, C, H, W, k, s, p,
                                       PAD[mode], gelu, nthr)
     else:
@@ -103,7 +106,25 @@ def test_emu_strip_path_large_primes(emu, shape, k, s, p, mode):
     x = rng.standard_normal(shape).astype(np.float32)
     w, b = orc.init_weight(shape[1], k, rng)
     ref = orc.converse2d_forward(x, w, b, s, p, mode, 1e-5, dtype=np.float64)
-    out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=96, strip=True)
+    out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=96, strip=True)     # Rader stages
+    assert orc.rel_l2(out, ref) <= 3e-5
+    out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=-96, strip=True)    # direct O(R^2) butterflies
+    assert orc.rel_l2(out, ref) <= 3e-5
+
+
+@pytest.mark.parametrize("shape,k,s,p,mode", [
+    ((3, 2, 30, 38), 5, 1, 2, "replicate"),   # 34 x 42: register radices, fused global stages
+    ((2, 1, 30, 38), 3, 2, 2, "circular"),    # upsampling epilogue with halo columns
+    ((3, 1, 54, 82), 5, 1, 2, "reflect"),     # 58 x 86: Rader first stages (29, 43)
+    ((1, 2, 54, 82), 2, 2, 2, "replicate"),
+])
+def test_emu_strip_compile_time_axis_plans(emu, shape, k, s, p, mode):
+    rng = np.random.default_rng(23)
+    x = rng.standard_normal(shape).astype(np.float32)
+    w, b = orc.init_weight(shape[1], k, rng)
+    ref = orc.converse2d_forward(x, w, b, s, p, mode, 1e-5, dtype=np.float64)
+    out = emu_forward(emu, x, w, b, s, p, mode, 1e-5, nthr=128, strip2=True)
+    assert np.isfinite(out).all()
     assert orc.rel_l2(out, ref) <= 3e-5
 
 
