@@ -26,6 +26,11 @@ int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_by
 // Same kernels, workspace = the library's own fixed device array (no allocation anywhere).
 int launch_strip_static_scratch(const FwdParams& P, int io_dtype, cudaStream_t st);
 
+// Fused channel-mixing kernels of ConverseBlock (k_block.cu).
+struct BlockParams;
+int launch_ln_pw_gelu(const BlockParams& P, int io_dtype, cudaStream_t st);
+int launch_pw_res_mlp(const BlockParams& P, int io_dtype, int sms, cudaStream_t st);
+
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;
 typedef int (*Strip2Launcher)(const StripParams& SP, int io_dtype, cudaStream_t st);

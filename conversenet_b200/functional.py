@@ -73,3 +73,44 @@ def converse2d_forward(x, table, weight_f32, kernel_size, scale, padding, paddin
                                     _stream_ptr(x.device))
     _cabi.check(rc, "cvb_converse2d_fwd")
     return out
+
+
+def _f32(t):
+    return t.detach().to(torch.float32).contiguous()
+
+
+def ln_pw_gelu(x, ln, conv):
+    """GELU(conv1x1(LayerNorm_channels_first(x))) in one kernel (C = 64 -> 128).
+    `ln`: the block's LayerNorm module, `conv`: its 1x1 nn.Conv2d (`models/util_converse.py:278-280`)."""
+    lib = _cabi.load()
+    x = x.contiguous()
+    B, C, H, W = x.shape
+    out = torch.empty((B, conv.out_channels, H, W), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.cvb_ln_pw_gelu_fwd(x.data_ptr(), out.data_ptr(), _f32(ln.weight).data_ptr(), _f32(ln.bias).data_ptr(),
+                                    float(ln.eps), _f32(conv.weight).data_ptr(), _f32(conv.bias).data_ptr(),
+                                    B, C, H * W, _io_dtype(x), _stream_ptr(x.device))
+    _cabi.check(rc, "cvb_ln_pw_gelu_fwd")
+    return out
+
+
+def pw_res_mlp(t, x, conv_out, ln, conv_up, conv_down, alpha1=None, alpha2=None):
+    """x1 = x + alpha1*conv_out(t); out = x1 + alpha2*conv_down(GELU(conv_up(LayerNorm(x1)))) in one kernel
+    (`models/util_converse.py:283-292`, alphas `:321-322`)."""
+    lib = _cabi.load()
+    t = t.contiguous()
+    x = x.contiguous()
+    B, C, H, W = x.shape
+    out = torch.empty_like(x)
+    keep = [_f32(conv_out.weight), _f32(conv_out.bias), _f32(ln.weight), _f32(ln.bias), _f32(conv_up.weight),
+            _f32(conv_up.bias), _f32(conv_down.weight), _f32(conv_down.bias)]
+    a1 = _f32(alpha1).reshape(-1) if alpha1 is not None else None
+    a2 = _f32(alpha2).reshape(-1) if alpha2 is not None else None
+    with torch.cuda.device(x.device):
+        rc = lib.cvb_pw_res_mlp_fwd(t.data_ptr(), x.data_ptr(), out.data_ptr(), keep[0].data_ptr(), keep[1].data_ptr(),
+                                    a1.data_ptr() if a1 is not None else None, keep[2].data_ptr(), keep[3].data_ptr(),
+                                    float(ln.eps), keep[4].data_ptr(), keep[5].data_ptr(), keep[6].data_ptr(),
+                                    keep[7].data_ptr(), a2.data_ptr() if a2 is not None else None,
+                                    B, C, H * W, _io_dtype(x), _stream_ptr(x.device))
+    _cabi.check(rc, "cvb_pw_res_mlp_fwd")
+    return out

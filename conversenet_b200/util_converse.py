@@ -149,7 +149,28 @@ class ConverseBlock(nn.Module):
             conv.fuse_gelu = False
         return c[5](t)
 
+    def _fusable(self, x):
+        c1, c2 = self.conv1, self.conv2
+        return (x.is_cuda and x.dim() == 4 and x.size(1) == 64 and c1[1].out_channels == 128 and
+                c1[5].out_channels == 64 and c1[3].scale == 1 and x.dtype in (torch.float32, torch.bfloat16) and
+                c1[1].bias is not None and c1[5].bias is not None and c2[1].bias is not None and
+                c2[3].bias is not None and os.environ.get("CVB_NO_BLOCK_FUSION", "") != "1")
+
+    def _forward_fused(self, x, alpha1=None, alpha2=None):
+        # three kernels per block: LN+1x1+GELU, Converse2D(+GELU), 1x1+residual+LN+1x1+GELU+1x1+residual
+        c1, c2 = self.conv1, self.conv2
+        t = CF.ln_pw_gelu(x, c1[0], c1[1])
+        conv = c1[3]
+        conv.fuse_gelu = True
+        try:
+            t = conv(t)
+        finally:
+            conv.fuse_gelu = False
+        return CF.pw_res_mlp(t, x, c1[5], c2[0], c2[1], c2[3], alpha1, alpha2)
+
     def forward(self, x):
+        if self._fusable(x):
+            return self._forward_fused(x)
         x = self._branch1(x) + x
         x = self.conv2(x) + x
         return x
@@ -165,6 +186,8 @@ class ConverseBlockAlphaVariant(ConverseBlock):
         self.alpha2 = nn.Parameter(torch.zeros((1, out_channels, 1, 1)), requires_grad=True)
 
     def forward(self, x):
+        if self._fusable(x):
+            return self._forward_fused(x, self.alpha1, self.alpha2)
         x = self.alpha1 * self._branch1(x) + x
         x = self.alpha2 * self.conv2(x) + x
         return x

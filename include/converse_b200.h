@@ -104,6 +104,27 @@ int cvb_converse2d_fwd(const void* x, void* out, const void* table, const float*
                        int fuse_gelu, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * ConverseBlock, first fused kernel: out = GELU( W . LayerNorm(x) + b ), C -> 2C channels,
+ * i.e. conv1[0..2] of the block: channels_first LayerNorm (models/util_converse.py:60-68),
+ * 1x1 Conv2d (:279), GELU (:280).  x (B,C,HW), out (B,2C,HW) contiguous, io_dtype;
+ * ln_w, ln_b (C); w (2C,C); b (2C), all fp32 device pointers.  C must be 64
+ * (CVB_ERR_UNSUPPORTED_SIZE otherwise).
+ */
+int cvb_ln_pw_gelu_fwd(const void* x, void* out, const float* ln_w, const float* ln_b, float ln_eps,
+                       const float* w, const float* b, int B, int C, int HW, int io_dtype, void* stream);
+
+/*
+ * ConverseBlock, second fused kernel (models/util_converse.py:283, 285-288, 291-292; alphas :321-322):
+ *   x1  = x + alpha1 * (W2 . t + b2)                              t (B,2C,HW): Converse2D output after GELU
+ *   out = x1 + alpha2 * (W4 . GELU(W3 . LayerNorm(x1) + b3) + b4)
+ * w2, w4 (C,2C); w3 (2C,C); b2, b4 (C); b3 (2C); alpha1, alpha2 (C) or NULL for 1.  C must be 64.
+ */
+int cvb_pw_res_mlp_fwd(const void* t, const void* x, void* out, const float* w2, const float* b2,
+                       const float* alpha1, const float* ln_w, const float* ln_b, float ln_eps,
+                       const float* w3, const float* b3, const float* w4, const float* b4,
+                       const float* alpha2, int B, int C, int HW, int io_dtype, void* stream);
+
+/*
  * Converse2D forward for callers that cannot allocate device memory.
  *
  * Same arguments, result and error codes as cvb_converse2d_fwd, minus the workspace:

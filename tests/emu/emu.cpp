@@ -7,6 +7,7 @@
 #include <cstdio>
 #include "../../conversenet_b200/csrc/cvb_plan.h"
 #include "../../conversenet_b200/csrc/cvb_strip2.cuh"
+#include "../../conversenet_b200/csrc/cvb_block.cuh"
 
 using namespace cvb;
 
@@ -146,6 +147,38 @@ int emu_converse2d_strip2(const float* x, float* out, const void* table, const f
   } else {
     return -100;
   }
+  return 0;
+}
+
+// Fused channel-mixing kernels of ConverseBlock, one emulated block of `nthr` threads at a time.
+int emu_ln_pw_gelu(const float* x, float* out, const float* ln_w, const float* ln_b, float eps, const float* w,
+                   const float* b, int B, int HW, int nthr) {
+  BlockParams P;
+  memset(&P, 0, sizeof(P));
+  P.x = x; P.out = out; P.ln_w = ln_w; P.ln_b = ln_b; P.ln_eps = eps; P.w_a = w; P.b_a = b; P.B = B; P.HW = HW;
+  std::vector<float> sm(kBlkC * kBlkM + kBlkM);
+  for (int t = 0; t < nthr; ++t) k1_stage(t, nthr, P, sm.data(), sm.data() + kBlkC * kBlkM);
+  const long long total = (long long)B * HW;
+  for (long long blk = 0; blk * nthr * 2 < total; ++blk)
+    for (int t = 0; t < nthr; ++t) {
+      const long long pix0 = blk * nthr * 2 + t;
+      if (pix0 < total) k1_pixels<float, 2>(P, sm.data(), sm.data() + kBlkC * kBlkM, pix0, nthr, total);
+    }
+  return 0;
+}
+
+int emu_pw_res_mlp(const float* t2, const float* x, float* out, const float* w2, const float* b2, const float* a1,
+                   const float* ln_w, const float* ln_b, float eps, const float* w3, const float* b3,
+                   const float* w4, const float* b4, const float* a2, int B, int HW, int nthr) {
+  BlockParams P;
+  memset(&P, 0, sizeof(P));
+  P.t = t2; P.x = x; P.out = out; P.ln_w = ln_w; P.ln_b = ln_b; P.ln_eps = eps;
+  P.w_a = w2; P.b_a = b2; P.w_b = w3; P.b_b = b3; P.w_c = w4; P.b_c = b4; P.alpha1 = a1; P.alpha2 = a2;
+  P.B = B; P.HW = HW;
+  std::vector<float> sm(k3_smem_floats());
+  const K3Smem m = k3_carve(sm.data());
+  for (int t = 0; t < nthr; ++t) k3_stage(t, nthr, P, m);
+  for (long long pix = 0; pix < (long long)B * HW; ++pix) k3_pixel<float>(P, m, pix);
   return 0;
 }
 

@@ -84,3 +84,29 @@ def test_conversenet_blind(fx):
     with torch.no_grad():
         out = m.cuda()(torch.from_numpy(fx["cnet_x"]).cuda()).cpu().numpy()
     _check(out, fx["cnet_ref32"], fx["cnet_ref64"])
+
+
+def test_fused_block_matches_unfused(monkeypatch):
+    # ConverseBlock through the three fused kernels vs the same module with torch's LayerNorm / 1x1 / GELU
+    from conversenet_b200 import ConverseBlock, ConverseBlockAlphaVariant
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for cls in (ConverseBlock, ConverseBlockAlphaVariant):
+        torch.manual_seed(3)
+        blk = cls(64, 64, kernel_size=5, padding=4, padding_mode="replicate").cuda().eval()
+        with torch.no_grad():
+            for n, p in blk.named_parameters():
+                if "alpha" in n:
+                    p.copy_(0.3 * torch.randn_like(p))
+                if n in ("conv1.0.weight", "conv2.0.weight", "conv1.0.bias", "conv2.0.bias"):
+                    p.add_(0.2 * torch.randn_like(p))
+        x = torch.randn(3, 64, 37, 29, device="cuda")
+        with torch.no_grad():
+            fused = blk(x)
+            monkeypatch.setenv("CVB_NO_BLOCK_FUSION", "1")
+            plain = blk(x)
+            monkeypatch.delenv("CVB_NO_BLOCK_FUSION")
+        assert float((fused - plain).norm() / plain.norm()) <= 5e-6
+        with torch.no_grad():
+            fb = blk(x.bfloat16()).float()
+        assert float((fb - plain).norm() / plain.norm()) <= 2e-2
