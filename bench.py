@@ -344,6 +344,139 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ whole networks (extra lines)
+MODEL_CFG = {
+    # name: (global batch, input shape per image, fp32 algorithmic GB per global batch with the
+    # fusion-forced accounting 11*C*H*W*e per ConverseBlock)
+    "dncnn": dict(batch=8, shape=(1, 256, 256), gbytes=29.8, desc="Converse-DnCNN, B8 x 1 x 256 x 256 (config 3)"),
+    "srresnet": dict(batch=16, shape=(3, 128, 128), gbytes=30.2, desc="Converse-SRResNet x4, B16 x 3 x 128 x 128 (config 4)"),
+    "usrnet": dict(batch=32, shape=(3, 512, 512), gbytes=853.0, desc="Converse-USRNet sf1, B32 x 3 x 512 x 512 (config 5)"),
+}
+
+
+def synthetic_images(name, n, seed):
+    """Seeded stand-ins for the missing image sets, with the value distributions of BASELINE.json."""
+    import numpy as np
+    from scipy.ndimage import gaussian_filter, uniform_filter
+    rng = np.random.default_rng(seed)
+    c, h, w = MODEL_CFG[name]["shape"]
+    if name == "dncnn":
+        f = gaussian_filter(rng.standard_normal((n, c, h, w)), sigma=(0, 0, 3, 3))
+        f = (f - f.min()) / (f.max() - f.min())
+        return (f + rng.standard_normal(f.shape) * 25.0 / 255.0).astype(np.float32)
+    if name == "srresnet":
+        return uniform_filter(rng.uniform(size=(n, c, h, w)), size=(1, 1, 3, 3)).astype(np.float32)
+    f = gaussian_filter(rng.standard_normal((n, c, h, w)), sigma=(0, 0, 4, 4))
+    f = (f - f.min()) / (f.max() - f.min())
+    return (f + rng.standard_normal(f.shape) * rng.uniform(0, 7.65 / 255.0)).astype(np.float32)
+
+
+def run_model(args):
+    """images/s of a whole network, the batch of the BASELINE config sharded over the ranks."""
+    import torch
+    import torch.distributed as dist
+    from conversenet_b200 import models
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    mc = MODEL_CFG[args.workload]
+    per_rank = max(1, mc["batch"] // world)
+    torch.manual_seed(0)
+    if args.workload == "dncnn":
+        net = models.ConverseDnCNN()
+    elif args.workload == "srresnet":
+        net = models.ConverseMSRResNet()
+    else:
+        net = models.ConverseUSRNet()
+        g = torch.Generator().manual_seed(1)
+        with torch.no_grad():  # the blocks are multiplied by alpha = 0 at init; give them weight
+            for n_, p_ in net.named_parameters():
+                if n_.endswith("alpha1") or n_.endswith("alpha2"):
+                    p_.copy_(0.1 * torch.randn(p_.shape, generator=g))
+    net = net.to(dev).eval()
+    tdtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    if tdtype != torch.float32:
+        net = net.to(tdtype)
+    xh = torch.from_numpy(synthetic_images(args.workload, per_rank, 100 + rank)).to(tdtype).pin_memory()
+    extra = ()
+    if args.workload == "usrnet":
+        kk = torch.rand(per_rank, 1, 7, 7, generator=torch.Generator().manual_seed(2))
+        extra = ((kk / kk.sum(dim=(-2, -1), keepdim=True)).to(dev), 1)
+    xd = xh.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K, W = args.steps, max(args.warmup, 3)
+    K = min(K, 20) if args.steps == 400 else K  # the default step count is sized for the single layer
+    with torch.no_grad():
+        for _ in range(W):
+            y = net(xd, *extra)
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            y = net(xd, *extra)
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        clocks = sampler.stop()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / K
+        # end to end: pinned host input in, host output back, every step
+        oh = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+        Ke = max(2, min(K, 5))
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        f0.record()
+        for _ in range(Ke):
+            oh.copy_(net(xh.to(dev, non_blocking=True), *extra), non_blocking=True)
+        f1.record()
+        torch.cuda.synchronize()
+        barrier()
+        te = torch.tensor([f0.elapsed_time(f1)], device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    images = per_rank * world
+    value = images / (ms_step * 1e-3)
+    peak, peak_kind = measured_peak_gbs()
+    esize = 4 if args.dtype == "fp32" else 2
+    gbytes = mc["gbytes"] * images / mc["batch"] * esize / 4.0
+    achieved = gbytes / world / (ms_step * 1e-3)
+    line = {
+        "metric": "model_throughput", "value": value, "unit": "images/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32" if args.dtype == "fp32" else "bf16-io/f32", "data": "synthetic",
+        "config": {"workload": mc["desc"], "global_batch": images, "per_rank_batch": per_rank,
+                   "sharding": "batch split over ranks, weights replicated, no collective",
+                   "l2": "activations of every layer exceed L2"},
+        "clocks": clocks,
+        "e2e": {"value": images / (float(te.item()) / Ke * 1e-3), "unit": "images/s",
+                "h2d_bytes_per_step": xh.numel() * xh.element_size(), "d2h_bytes_per_step": oh.numel() * oh.element_size(),
+                "steps": Ke},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_kind,
+                     "note": "whole-network figure: fusion-forced algorithmic bytes / step time"},
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def read_traffic():
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
     try:
@@ -360,12 +493,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "dncnn", "srresnet", "usrnet"],
+                    help="cfg2 (default, the headline line) or a whole network of BASELINE.json configs 3-5")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "cfg2":
+        run_model(args)
     else:
         run_ours(args)
 
