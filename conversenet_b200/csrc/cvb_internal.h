@@ -30,6 +30,8 @@ int launch_strip_static_scratch(const FwdParams& P, int io_dtype, cudaStream_t s
 struct BlockParams;
 int launch_ln_pw_gelu(const BlockParams& P, int io_dtype, cudaStream_t st);
 int launch_pw_res_mlp(const BlockParams& P, int io_dtype, int sms, cudaStream_t st);
+// tcgen05 variant of the first kernel (k_block_tc.cu): fp32, HW a multiple of 128
+int launch_ln_pw_gelu_tc(const BlockParams& P, int sms, int* status, cudaStream_t st);
 
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;

@@ -52,6 +52,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 #else
+inline uint32_t smem_u32(const void*) { return 0; }
 inline void mbar_init(uint64_t*, int) {}
 inline void mbar_fence_init() {}
 inline void mbar_expect_tx(uint64_t*, uint32_t) {}

@@ -110,3 +110,30 @@ def test_fused_block_matches_unfused(monkeypatch):
         with torch.no_grad():
             fb = blk(x.bfloat16()).float()
         assert float((fb - plain).norm() / plain.norm()) <= 2e-2
+
+
+def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
+    # LN + 1x1 + GELU on tcgen05 (TF32 hi/lo split, three MMAs per product) vs the fp32 CUDA-core kernel
+    from conversenet_b200 import functional as CF, _cabi
+    from conversenet_b200.util_converse import LayerNorm
+    torch.manual_seed(5)
+    ln = LayerNorm(64, eps=1e-5, data_format="channels_first").cuda()
+    conv = torch.nn.Conv2d(64, 128, 1).cuda()
+    with torch.no_grad():
+        ln.weight.add_(0.3 * torch.randn_like(ln.weight))
+        ln.bias.add_(0.2 * torch.randn_like(ln.bias))
+    x = torch.randn(3, 64, 64, 96, device="cuda")   # 6144 pixels per image: whole 128-pixel tiles
+    monkeypatch.setenv("CVB_TC", "0")
+    ref = CF.ln_pw_gelu(x, ln, conv)
+    monkeypatch.setenv("CVB_TC", "1")
+    out = CF.ln_pw_gelu(x, ln, conv)
+    torch.cuda.synchronize()
+    assert _cabi.load().cvb_last_device_status(1) == 0
+    assert float((out - ref).norm() / ref.norm()) <= 3e-6
+    # torch fp32 reference of the same op
+    u = x.mean(1, keepdim=True)
+    s = (x - u).pow(2).mean(1, keepdim=True)
+    xn = ln.weight[:, None, None] * ((x - u) / torch.sqrt(s + 1e-5)) + ln.bias[:, None, None]
+    torch.backends.cudnn.allow_tf32 = False
+    want = torch.nn.functional.gelu(conv(xn))
+    assert float((out - want).norm() / want.norm()) <= 5e-6
