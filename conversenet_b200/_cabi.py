@@ -30,6 +30,7 @@ SIGNATURES = {
                                           [_c.c_int] * 10 + [_c.c_void_p]),
     "cvb_ln_pw_gelu_fwd": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_float] + [_c.c_void_p] * 2 + [_c.c_int] * 4 + [_c.c_void_p]),
     "cvb_pw_res_mlp_fwd": (_c.c_int, [_c.c_void_p] * 8 + [_c.c_float] + [_c.c_void_p] * 5 + [_c.c_int] * 4 + [_c.c_void_p]),
+    "cvb_pw_res_fwd": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 4 + [_c.c_void_p]),
     "cvb_plan_radices": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int), _c.c_int]),
     "cvb_fits_shared": (_c.c_int, [_c.c_int, _c.c_int]),
 }

@@ -32,6 +32,8 @@ int launch_ln_pw_gelu(const BlockParams& P, int io_dtype, cudaStream_t st);
 int launch_pw_res_mlp(const BlockParams& P, int io_dtype, int sms, cudaStream_t st);
 // tcgen05 variant of the first kernel (k_block_tc.cu): fp32, HW a multiple of 128
 int launch_ln_pw_gelu_tc(const BlockParams& P, int sms, int* status, cudaStream_t st);
+// tcgen05: out = res + alpha * (W . t + b), 128 -> 64 channels (P.t, P.x = res, P.w_a, P.b_a, P.alpha1)
+int launch_pw_res_tc(const BlockParams& P, int sms, int* status, cudaStream_t st);
 
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;

@@ -1,4 +1,6 @@
 """Tensor-level entry points over the C ABI (device memory and streams come from torch)."""
+import os
+
 import torch
 
 from . import _cabi
@@ -101,6 +103,11 @@ def pw_res_mlp(t, x, conv_out, ln, conv_up, conv_down, alpha1=None, alpha2=None)
     t = t.contiguous()
     x = x.contiguous()
     B, C, H, W = x.shape
+    if (x.dtype == torch.float32 and (H * W) % 128 == 0 and os.environ.get("CVB_TC", "1") != "0"):
+        # tensor-core route: three tcgen05 kernels (1x1 + residual, LN + 1x1 + GELU, 1x1 + residual)
+        x1 = pw_res(t, x, conv_out, alpha1)
+        hid = ln_pw_gelu(x1, ln, conv_up)
+        return pw_res(hid, x1, conv_down, alpha2)
     out = torch.empty_like(x)
     keep = [_f32(conv_out.weight), _f32(conv_out.bias), _f32(ln.weight), _f32(ln.bias), _f32(conv_up.weight),
             _f32(conv_up.bias), _f32(conv_down.weight), _f32(conv_down.bias)]
@@ -113,4 +120,21 @@ def pw_res_mlp(t, x, conv_out, ln, conv_up, conv_down, alpha1=None, alpha2=None)
                                     keep[7].data_ptr(), a2.data_ptr() if a2 is not None else None,
                                     B, C, H * W, _io_dtype(x), _stream_ptr(x.device))
     _cabi.check(rc, "cvb_pw_res_mlp_fwd")
+    return out
+
+
+def pw_res(t, res, conv, alpha=None):
+    """res + alpha * conv1x1(t) on the tensor cores (128 -> 64 channels, fp32, whole 128-pixel tiles)."""
+    lib = _cabi.load()
+    t = t.contiguous()
+    res = res.contiguous()
+    B, C, H, W = res.shape
+    out = torch.empty_like(res)
+    w, b = _f32(conv.weight), _f32(conv.bias)
+    a = _f32(alpha).reshape(-1) if alpha is not None else None
+    with torch.cuda.device(res.device):
+        rc = lib.cvb_pw_res_fwd(t.data_ptr(), res.data_ptr(), out.data_ptr(), w.data_ptr(), b.data_ptr(),
+                                a.data_ptr() if a is not None else None, B, C, H * W, _io_dtype(res),
+                                _stream_ptr(res.device))
+    _cabi.check(rc, "cvb_pw_res_fwd")
     return out
