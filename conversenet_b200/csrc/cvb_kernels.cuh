@@ -929,8 +929,9 @@ struct TransferParams {
   RaderInfo ry, rx;
 };
 
-// One table entry: position (posx, posy) of channel c.  fp64 throughout.
-__host__ __device__ inline void transfer_entry(const TransferParams& T, int c, int posy, int posx) {
+// One table entry, straightforward form (one sine / cosine pair per tap and alias); kept for
+// scales above kFastMaxScale.  fp64 throughout.
+__host__ __device__ inline void transfer_entry_slow(const TransferParams& T, int c, int posy, int posx) {
   const int s = T.s, k = T.k, h = T.h, w = T.w, cc = T.k / 2;
   const int u = pos_to_freq(T.py, posy), v = pos_to_freq(T.px, posx);
   const double lam = 1.0 / (1.0 + exp(-((double)T.bias[c] - 9.0))) + (double)T.eps;
@@ -974,6 +975,107 @@ __host__ __device__ inline void transfer_entry(const TransferParams& T, int c, i
         num_r = fr; num_i = -fi;  // conj(FK)
       } else {
         const double dr = dhr * dwr - dhi * dwi, di = dhr * dwi + dhi * dwr;
+        num_r += fr * dr - fi * di;
+        num_i += fr * di + fi * dr;
+      }
+    }
+  }
+  const double inv_alias = 1.0 / (double)(s * s);
+  const double norm = 1.0 / ((double)h * (double)w);
+  double tr, ti;
+  if (s == 1) {
+    const double d = den + lam;
+    tr = (num_r + lam) / d;
+    ti = num_i / d;
+  } else {
+    const double d = den * inv_alias + lam;
+    tr = (1.0 - num_r * inv_alias) / d;
+    ti = (-num_i * inv_alias) / d;
+  }
+  T.table[((size_t)c * w + posx) * h + posy] = make_float2((float)(tr * norm), (float)(ti * norm));
+}
+
+// exp(-2 pi i m / N) in fp64
+__host__ __device__ inline void cis_neg(long long m, int N, double& cr, double& ci) {
+#ifdef __CUDA_ARCH__
+  double sn, cs;
+  sincospi(-2.0 * (double)m / (double)N, &sn, &cs);
+  cr = cs; ci = sn;
+#else
+  const double a = -2.0 * M_PI * (double)m / (double)N;
+  cr = cos(a); ci = sin(a);
+#endif
+}
+
+constexpr int kFastMaxScale = 4;
+
+// One table entry: position (posx, posy) of channel c.  fp64 throughout.  The kernel spectrum is
+// separable in its exponentials: with ey = exp(-2 pi i U / Nh), ex = exp(-2 pi i V / Nw),
+//   FK[U,V] = sum_a ey^(a-c) * ( sum_b K[a][b] * ex^(b-c) ),
+// so one sine / cosine pair per axis and alias and k*k real-by-complex multiply-adds per alias
+// replace a sine / cosine pair per tap.  (The per-sample data step of USRNet rebuilds this table
+// at every call, models/converse_usrnet.py:203-211, so its cost is on the hot path there.)
+__host__ __device__ inline void transfer_entry(const TransferParams& T, int c, int posy, int posx) {
+  const int s = T.s, k = T.k, h = T.h, w = T.w, cc = T.k / 2;
+  if (s > kFastMaxScale) {
+    transfer_entry_slow(T, c, posy, posx);
+    return;
+  }
+  const int u = pos_to_freq(T.py, posy), v = pos_to_freq(T.px, posx);
+  const double lam = 1.0 / (1.0 + exp(-((double)T.bias[c] - 9.0))) + (double)T.eps;
+  const int Nh = s * h, Nw = s * w;
+  const float* K = T.weight + (size_t)c * k * k;
+  // per alias along x: tx[ib][a] = sum_b K[a][b] ex^(b-c), and the box factor D_w
+  double txr[kFastMaxScale][kMaxTaps], txi[kFastMaxScale][kMaxTaps], dwr[kFastMaxScale], dwi[kFastMaxScale];
+  for (int ib = 0; ib < s; ++ib) {
+    const int V = v + ib * w;
+    double er, ei, pr, pi;
+    cis_neg(V, Nw, er, ei);
+    // ex^(-c)
+    cis_neg((long long)(-cc) * V % Nw + ((long long)(-cc) * V % Nw < 0 ? Nw : 0), Nw, pr, pi);
+    for (int a = 0; a < k; ++a) { txr[ib][a] = 0.0; txi[ib][a] = 0.0; }
+    for (int b = 0; b < k; ++b) {
+      for (int a = 0; a < k; ++a) {
+        const double kv = (double)K[a * k + b];
+        txr[ib][a] += kv * pr;
+        txi[ib][a] += kv * pi;
+      }
+      const double nr = pr * er - pi * ei, ni = pr * ei + pi * er;
+      pr = nr; pi = ni;
+    }
+    double sr = 0.0, si = 0.0, qr = 1.0, qi = 0.0;  // D_w = sum_{b<s} ex^b
+    for (int b = 0; b < s; ++b) {
+      sr += qr; si += qi;
+      const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
+      qr = nr; qi = ni;
+    }
+    dwr[ib] = sr; dwi[ib] = si;
+  }
+  double num_r = 0.0, num_i = 0.0, den = 0.0;
+  for (int ia = 0; ia < s; ++ia) {
+    const int U = u + ia * h;
+    double er, ei, p0r, p0i;
+    cis_neg(U, Nh, er, ei);
+    cis_neg((long long)(-cc) * U % Nh + ((long long)(-cc) * U % Nh < 0 ? Nh : 0), Nh, p0r, p0i);
+    double dhr = 0.0, dhi = 0.0, qr = 1.0, qi = 0.0;  // D_h = sum_{a<s} ey^a
+    for (int a = 0; a < s; ++a) {
+      dhr += qr; dhi += qi;
+      const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
+      qr = nr; qi = ni;
+    }
+    for (int ib = 0; ib < s; ++ib) {
+      double fr = 0.0, fi = 0.0, pr = p0r, pi = p0i;
+      for (int a = 0; a < k; ++a) {
+        fr += pr * txr[ib][a] - pi * txi[ib][a];
+        fi += pr * txi[ib][a] + pi * txr[ib][a];
+        const double nr = pr * er - pi * ei, ni = pr * ei + pi * er;
+        pr = nr; pi = ni;
+      }
+      den += fr * fr + fi * fi;
+      if (s == 1) {
+        num_r = fr; num_i = -fi;  // conj(FK)
+      } else {
+        const double dr = dhr * dwr[ib] - dhi * dwi[ib], di = dhr * dwi[ib] + dhi * dwr[ib];
         num_r += fr * dr - fi * di;
         num_i += fr * di + fi * dr;
       }
