@@ -67,6 +67,7 @@ struct PassArgs {
   const float2* tw;    // tw[n] = (cos, sin)(2 pi n / N)
   float inv_nlines, invM;
   int nl1, ls2;        // nl1 > 0: lines form a 2-level grid, line -> (line % nl1) * ls + (line / nl1) * ls2
+  float inv_nl1;
   const float2* tab;   // PASS_MID multiplier when not the per-channel transfer table (else null)
   int tab_es, tab_ls;  //   its strides along the transform axis / across lines
 };
@@ -176,7 +177,12 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
       divmod_small(t, a.M, a.invM, blk, j);
     }
     const int base = blk * aL + j;
-    const int loff = a.nl1 > 0 ? (line % a.nl1) * a.ls + (line / a.nl1) * a.ls2 : line * a.ls;
+    int loff = line * a.ls;
+    if (a.nl1 > 0) {
+      int l2, l1;
+      divmod_small(line, a.nl1, a.inv_nl1, l2, l1);
+      loff = l1 * a.ls + l2 * a.ls2;
+    }
     float2* ptr = a.sm + loff + base * a.es;
     const int st = aM * a.es;
     const int tstep = j * atws;
@@ -308,7 +314,7 @@ CVB_HD PassArgs make_pass(float2* sm, bool along_y, int pitch, int h, int w, int
   a.tw = tw;
   a.inv_nlines = 1.0f / (float)a.nlines;
   a.invM = 1.0f / (float)M;
-  a.nl1 = 0; a.ls2 = 0;
+  a.nl1 = 0; a.ls2 = 0; a.inv_nl1 = 0.f;
   a.tab = nullptr; a.tab_es = 0; a.tab_ls = 0;
   return a;
 }

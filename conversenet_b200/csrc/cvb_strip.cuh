@@ -139,22 +139,24 @@ CVB_HD RaderSmem rader_views(const float2* base, int R) {
 }
 
 // gather: oth[p = q+1] = x[g^q] (pre-twiddled by W_N^(j p) for an inverse-type stage), oth[0] = x[0]
+template <int CM = 0>
 CVB_HD void rader_gather(int tid, int nthr, const float2* cur, float2* oth, const PassArgs& a, int R,
                          const RaderSmem& rs, bool pre) {
-  const int total = a.nlines * a.M * R;
+  const int aM = CM ? CM : a.M;
+  const int total = a.nlines * aM * R;
   const float inv_nl = 1.0f / (float)a.nlines;
   for (int wi = tid; wi < total; wi += nthr) {
     int rest, line;
     divmod_small(wi, a.nlines, inv_nl, rest, line);
-    const int q = rest / a.M, j = rest - q * a.M;  // q = 0 .. R-1; q == R-1 stands for element 0
+    const int q = rest / aM, j = rest - q * aM;  // q = 0 .. R-1; q == R-1 stands for element 0
     const int src_p = (q == R - 1) ? 0 : rs.perm_in[q];
     const int dst_p = (q == R - 1) ? 0 : q + 1;
-    float2 v = cur[line * a.ls + (j + src_p * a.M) * a.es];
+    float2 v = cur[line * a.ls + (j + src_p * aM) * a.es];
     if (pre && src_p != 0 && j != 0) {
       const float2 wv = a.tw[j * src_p * a.tws];
       v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
     }
-    oth[line * a.ls + (j + dst_p * a.M) * a.es] = v;
+    oth[line * a.ls + (j + dst_p * aM) * a.es] = v;
   }
 }
 
@@ -176,17 +178,19 @@ CVB_HD void rader_dc(int tid, int nthr, float2* cur, const float2* oth, const Pa
 }
 
 // scatter: X[g^-m] = x_0 + conj(c_m), post-twiddled by W_N^(j k) for a forward stage
+template <int CM = 0>
 CVB_HD void rader_scatter(int tid, int nthr, float2* cur, const float2* oth, const PassArgs& a, int R,
                           const RaderSmem& rs, bool post, float osign) {
-  const int total = a.nlines * a.M * (R - 1);
+  const int aM = CM ? CM : a.M;
+  const int total = a.nlines * aM * (R - 1);
   const float inv_nl = 1.0f / (float)a.nlines;
   for (int wi = tid; wi < total; wi += nthr) {
     int rest, line;
     divmod_small(wi, a.nlines, inv_nl, rest, line);
-    const int m = rest / a.M, j = rest - m * a.M;
+    const int m = rest / aM, j = rest - m * aM;
     const float2* ip = oth + line * a.ls + j * a.es;
     const float2 x0 = ip[0];
-    const float2 c = ip[(m + 1) * a.M * a.es];
+    const float2 c = ip[(m + 1) * aM * a.es];
     float vr = x0.x + c.x, vi = x0.y - c.y;
     const int k = rs.perm_out[m];
     if (post && j != 0) {
@@ -194,7 +198,7 @@ CVB_HD void rader_scatter(int tid, int nthr, float2* cur, const float2* oth, con
       const float tr = fmaf(vi, wv.y, vr * wv.x), ti = fmaf(-vr, wv.y, vi * wv.x);
       vr = tr; vi = ti;
     }
-    cur[line * a.ls + (j + k * a.M) * a.es] = make_float2(vr, osign * vi);
+    cur[line * a.ls + (j + k * aM) * a.es] = make_float2(vr, osign * vi);
   }
 }
 
@@ -204,6 +208,7 @@ CVB_HD PassArgs rader_sub_pass(float2* oth, const PassArgs& a, const RaderInfo& 
   s.sm = oth + a.M * a.es;          // element p = 1 of every sub-line
   s.es = a.M * a.es;
   s.nl1 = a.nlines;                 // sub-line (line, j): offset line * ls + j * (outer es)
+  s.inv_nl1 = 1.0f / (float)a.nlines;
   s.ls2 = a.es;
   s.nlines = a.nlines * a.M;
   s.inv_nlines = 1.0f / (float)s.nlines;

@@ -33,24 +33,119 @@ CVB_HD size_t strip2_smem(int N, int lines, int R0, int k) {
   return f2 * sizeof(float2);
 }
 
-// Rader stage with a compile-time sub-plan R - 1 = S0 * S1 (see rader_* in cvb_strip.cuh)
-#define CVB_RADER_STATIC(R, S0, S1, cur, oth, a_, rinfo, rsm, pre_, osg_)                                   \
+// ---- Rader stage with a compile-time sub-plan R - 1 = S0 * S1, gather and scatter fused ----
+// Three phases: (1) X_0 by a direct sum + first sub-stage reading its inputs through the g^q
+// permutation straight from the tile; (2) second sub-stage with the B-hat multiply and its inverse
+// (fft_pass, PASS_MID); (3) inverse first sub-stage writing x_0 + conj(c_m) through the g^-m permutation
+// back into the tile.  `oth` holds the length-(R-1) sequences (element p = e + 1) and x_0 at p = 0.
+template <int CM>
+CVB_HD void rader_dc_fused(int tid, int nthr, float2* cur, float2* oth, const PassArgs& a, int R, bool pre,
+                           float osign) {
+  const int total = a.nlines * CM;
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int j, line;
+    divmod_small(wi, a.nlines, inv_nl, j, line);
+    float2* ip = cur + line * a.ls + j * a.es;
+    const float2 x0 = ip[0];
+    float sr = x0.x, si = x0.y;
+    for (int p = 1; p < R; ++p) {
+      float2 v = ip[p * CM * a.es];
+      if (pre && j != 0) {
+        const float2 wv = a.tw[j * p * a.tws];
+        v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
+      }
+      sr += v.x; si += v.y;
+    }
+    oth[line * a.ls + j * a.es] = x0;
+    ip[0] = make_float2(sr, osign * si);
+  }
+}
+
+template <int S0, int S1, int CM>
+CVB_HD void rader_first_pass(int tid, int nthr, const float2* cur, float2* oth, const PassArgs& a, int R,
+                             const RaderSmem& rs, bool pre) {
+  const int total = a.nlines * CM * S1;
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int rest, line;
+    divmod_small(wi, a.nlines, inv_nl, rest, line);
+    const int jp = rest / CM, jj = rest - jp * CM;   // butterfly of the sub-transform, outer j
+    const float2* bc = cur + line * a.ls + jj * a.es;
+    float2* bo = oth + line * a.ls + (jj + CM) * a.es;
+    float re[S0], im[S0];
+#pragma unroll
+    for (int q = 0; q < S0; ++q) {
+      const int p = rs.perm_in[jp + S1 * q];
+      float2 v = bc[p * CM * a.es];
+      if (pre && jj != 0) {
+        const float2 wv = a.tw[jj * p * a.tws];
+        v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
+      }
+      re[q] = v.x; im[q] = v.y;
+    }
+    Radix<S0>::fwd(re, im);
+#pragma unroll
+    for (int q = 1; q < S0; ++q) {
+      const float2 wv = rs.tw[jp * q];
+      const float xr = re[q], xi = im[q];
+      re[q] = fmaf(xi, wv.y, xr * wv.x);
+      im[q] = fmaf(-xr, wv.y, xi * wv.x);
+    }
+#pragma unroll
+    for (int q = 0; q < S0; ++q) bo[(jp + S1 * q) * CM * a.es] = make_float2(re[q], im[q]);
+  }
+}
+
+template <int S0, int S1, int CM>
+CVB_HD void rader_last_pass(int tid, int nthr, float2* cur, const float2* oth, const PassArgs& a, int R,
+                            const RaderSmem& rs, bool post, float osign) {
+  const int total = a.nlines * CM * S1;
+  const float inv_nl = 1.0f / (float)a.nlines;
+  for (int wi = tid; wi < total; wi += nthr) {
+    int rest, line;
+    divmod_small(wi, a.nlines, inv_nl, rest, line);
+    const int jp = rest / CM, jj = rest - jp * CM;
+    const float2* bo = oth + line * a.ls + (jj + CM) * a.es;
+    float2* bc = cur + line * a.ls + jj * a.es;
+    const float2 x0 = oth[line * a.ls + jj * a.es];
+    float re[S0], im[S0];
+#pragma unroll
+    for (int q = 0; q < S0; ++q) {
+      const float2 v = bo[(jp + S1 * q) * CM * a.es];
+      re[q] = v.x; im[q] = v.y;
+    }
+#pragma unroll
+    for (int q = 1; q < S0; ++q) {
+      const float2 wv = rs.tw[jp * q];
+      const float xr = re[q], xi = im[q];
+      re[q] = fmaf(xi, wv.y, xr * wv.x);
+      im[q] = fmaf(-xr, wv.y, xi * wv.x);
+    }
+    Radix<S0>::fwd(re, im);
+#pragma unroll
+    for (int q = 0; q < S0; ++q) {
+      const int k = rs.perm_out[jp + S1 * q];
+      float vr = x0.x + re[q], vi = x0.y - im[q];   // x_0 + conj(c_m)
+      if (post && jj != 0) {
+        const float2 wv = a.tw[jj * k * a.tws];
+        const float tr = fmaf(vi, wv.y, vr * wv.x), ti = fmaf(-vr, wv.y, vi * wv.x);
+        vr = tr; vi = ti;
+      }
+      bc[k * CM * a.es] = make_float2(vr, osign * vi);
+    }
+  }
+}
+
+#define CVB_RADER_STATIC(R, R1_, S0, S1, cur, oth, a_, rinfo, rsm, pre_, osg_)                              \
   do {                                                                                                    \
-    CVB_PHASE(rader_gather(tid, nthr, cur, oth, a_, R, rsm, pre_));                                       \
-    CVB_PHASE(rader_dc(tid, nthr, cur, oth, a_, R, osg_));                                                \
-    {                                                                                                     \
-      const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, 0, rsm);                                         \
-      CVB_PHASE((fft_pass<S0, float, R - 1, R - 1, S1, 0, 0>(tid, nthr, s_, io, 0)));                     \
-    }                                                                                                     \
+    CVB_PHASE((rader_dc_fused<R1_>(tid, nthr, cur, oth, a_, R, pre_, osg_),                               \
+               rader_first_pass<S0, S1, R1_>(tid, nthr, cur, oth, a_, R, rsm, pre_)));                    \
     {                                                                                                     \
       const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, 1, rsm);                                         \
       CVB_PHASE((fft_pass<S1, float, R - 1, S1, 1, 0, PASS_MID>(tid, nthr, s_, io, 0)));                  \
     }                                                                                                     \
-    {                                                                                                     \
-      const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, 0, rsm);                                         \
-      CVB_PHASE((fft_pass<S0, float, R - 1, R - 1, S1, 0, PASS_PRE>(tid, nthr, s_, io, 0)));              \
-    }                                                                                                     \
-    CVB_PHASE(rader_scatter(tid, nthr, cur, oth, a_, R, rsm, !(pre_), osg_));                             \
+    CVB_PHASE((rader_last_pass<S0, S1, R1_>(tid, nthr, cur, oth, a_, R, rsm, !(pre_), osg_)));            \
   } while (0)
 
 CVB_HD PassArgs strip_pass(float2* tile, int tp, int nlines, int N, int L, int M, const float2* tw) {
@@ -193,7 +288,7 @@ __host__ __device__ void strip2_A_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
                copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, rader_floats2(R0)),
                tile_load_x<IO>(tid, nthr, m.cur, tp, nc, x0, P, io)));
-    CVB_RADER_STATIC(R0, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, false, 1.0f);
+    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, false, 1.0f);
   }
   CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
   CVB_PHASE(tileT_to_ws(tid, nthr, m.cur, tp, h, nc, ST, x0));
@@ -233,9 +328,9 @@ __host__ __device__ void strip2_B_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob + h, w),
                copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.rx.off, rader_floats2(R0)),
                tile_rows_from_ws(tid, nthr, m.cur, tp, w, nc, ST, h, y0)));
-    CVB_RADER_STATIC(R0, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, false, 1.0f);
+    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, false, 1.0f);
     CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
-    CVB_RADER_STATIC(R0, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, true, 1.0f);
+    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, true, 1.0f);
     CVB_PHASE(tile_rows_to_ws(tid, nthr, m.cur, tp, w, nc, ST, h, y0));
   }
 }
@@ -278,7 +373,7 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
       CVB_PHASE(tile_epilogue<IO>(tid, nthr, m.cur, tp, nc, x0, hl, m.wk, P, io));
     }
   } else {
-    CVB_RADER_STATIC(R0, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, true, -1.0f);
+    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, true, -1.0f);
     if (P.s == 1) {
       CVB_PHASE(tile_store_crop<IO>(tid, nthr, m.cur, tp, nc, x0, P, io));
     } else {
