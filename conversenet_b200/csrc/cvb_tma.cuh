@@ -26,6 +26,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // global -> this block's shared memory, completion counted in bytes on `bar`
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile(
@@ -56,7 +59,9 @@ inline uint32_t smem_u32(const void*) { return 0; }
 inline void mbar_init(uint64_t*, int) {}
 inline void mbar_fence_init() {}
 inline void mbar_expect_tx(uint64_t*, uint32_t) {}
+inline void mbar_arrive(uint64_t*) {}
 inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t*) { memcpy(dst, src, bytes); }
+inline bool mbar_try_wait(uint64_t*, uint32_t) { return true; }
 inline bool mbar_wait_bounded(uint64_t*, uint32_t, int) { return true; }
 #endif
 

@@ -125,11 +125,25 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
     x = torch.randn(3, 64, 64, 96, device="cuda")   # 6144 pixels per image: whole 128-pixel tiles
     monkeypatch.setenv("CVB_TC", "0")
     ref = CF.ln_pw_gelu(x, ln, conv)
-    monkeypatch.setenv("CVB_TC", "1")
+    monkeypatch.setenv("CVB_TC", "1")    # single-buffered kernel
+    out1 = CF.ln_pw_gelu(x, ln, conv)
+    monkeypatch.setenv("CVB_TC", "2")    # warp-specialised, double-buffered kernel (the default)
     out = CF.ln_pw_gelu(x, ln, conv)
     torch.cuda.synchronize()
     assert _cabi.load().cvb_last_device_status(1) == 0
+    assert float((out1 - ref).norm() / ref.norm()) <= 3e-6
     assert float((out - ref).norm() / ref.norm()) <= 3e-6
+    # 1x1 + residual (128 -> 64) on the tensor cores against PyTorch
+    conv2 = torch.nn.Conv2d(128, 64, 1).cuda()
+    alpha = torch.randn(1, 64, 1, 1, device="cuda")
+    t = torch.randn(3, 128, 64, 96, device="cuda")
+    torch.backends.cudnn.allow_tf32 = False
+    want2 = x + alpha * conv2(t)
+    for mode in ("1", "2"):
+        monkeypatch.setenv("CVB_TC", mode)
+        got2 = CF.pw_res(t, x, conv2, alpha)
+        assert float((got2 - want2).norm() / want2.norm()) <= 5e-6
+    assert _cabi.load().cvb_last_device_status(1) == 0
     # torch fp32 reference of the same op
     u = x.mean(1, keepdim=True)
     s = (x - u).pow(2).mean(1, keepdim=True)
