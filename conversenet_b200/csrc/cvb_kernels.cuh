@@ -1021,8 +1021,11 @@ constexpr int kFastMaxScale = 4;
 // so one sine / cosine pair per axis and alias and k*k real-by-complex multiply-adds per alias
 // replace a sine / cosine pair per tap.  (The per-sample data step of USRNet rebuilds this table
 // at every call, models/converse_usrnet.py:203-211, so its cost is on the hot path there.)
-__host__ __device__ inline void transfer_entry(const TransferParams& T, int c, int posy, int posx) {
-  const int s = T.s, k = T.k, h = T.h, w = T.w, cc = T.k / 2;
+// CK, CS: compile-time kernel size and scale (0 = run-time values): with both known the small
+// per-alias arrays live in registers.
+template <int CK, int CS>
+__host__ __device__ inline void transfer_entry_t(const TransferParams& T, int c, int posy, int posx) {
+  const int s = CS ? CS : T.s, k = CK ? CK : T.k, h = T.h, w = T.w, cc = k / 2;
   if (s > kFastMaxScale) {
     transfer_entry_slow(T, c, posy, posx);
     return;
@@ -1032,16 +1035,21 @@ __host__ __device__ inline void transfer_entry(const TransferParams& T, int c, i
   const int Nh = s * h, Nw = s * w;
   const float* K = T.weight + (size_t)c * k * k;
   // per alias along x: tx[ib][a] = sum_b K[a][b] ex^(b-c), and the box factor D_w
-  double txr[kFastMaxScale][kMaxTaps], txi[kFastMaxScale][kMaxTaps], dwr[kFastMaxScale], dwi[kFastMaxScale];
-  for (int ib = 0; ib < s; ++ib) {
+  constexpr int AS = CS ? CS : kFastMaxScale, AK = CK ? CK : kMaxTaps;
+  double txr[AS][AK], txi[AS][AK], dwr[AS], dwi[AS];
+#pragma unroll
+  for (int ib = 0; ib < (CS ? CS : s); ++ib) {
     const int V = v + ib * w;
     double er, ei, pr, pi;
     cis_neg(V, Nw, er, ei);
     // ex^(-c)
     cis_neg((long long)(-cc) * V % Nw + ((long long)(-cc) * V % Nw < 0 ? Nw : 0), Nw, pr, pi);
-    for (int a = 0; a < k; ++a) { txr[ib][a] = 0.0; txi[ib][a] = 0.0; }
-    for (int b = 0; b < k; ++b) {
-      for (int a = 0; a < k; ++a) {
+#pragma unroll
+    for (int a = 0; a < (CK ? CK : k); ++a) { txr[ib][a] = 0.0; txi[ib][a] = 0.0; }
+#pragma unroll
+    for (int b = 0; b < (CK ? CK : k); ++b) {
+#pragma unroll
+      for (int a = 0; a < (CK ? CK : k); ++a) {
         const double kv = (double)K[a * k + b];
         txr[ib][a] += kv * pr;
         txi[ib][a] += kv * pi;
@@ -1058,7 +1066,8 @@ __host__ __device__ inline void transfer_entry(const TransferParams& T, int c, i
     dwr[ib] = sr; dwi[ib] = si;
   }
   double num_r = 0.0, num_i = 0.0, den = 0.0;
-  for (int ia = 0; ia < s; ++ia) {
+#pragma unroll
+  for (int ia = 0; ia < (CS ? CS : s); ++ia) {
     const int U = u + ia * h;
     double er, ei, p0r, p0i;
     cis_neg(U, Nh, er, ei);
@@ -1069,9 +1078,11 @@ __host__ __device__ inline void transfer_entry(const TransferParams& T, int c, i
       const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
       qr = nr; qi = ni;
     }
-    for (int ib = 0; ib < s; ++ib) {
+#pragma unroll
+    for (int ib = 0; ib < (CS ? CS : s); ++ib) {
       double fr = 0.0, fi = 0.0, pr = p0r, pi = p0i;
-      for (int a = 0; a < k; ++a) {
+#pragma unroll
+      for (int a = 0; a < (CK ? CK : k); ++a) {
         fr += pr * txr[ib][a] - pi * txi[ib][a];
         fi += pr * txi[ib][a] + pi * txr[ib][a];
         const double nr = pr * er - pi * ei, ni = pr * ei + pi * er;
@@ -1101,6 +1112,163 @@ __host__ __device__ inline void transfer_entry(const TransferParams& T, int c, i
   }
   T.table[((size_t)c * w + posx) * h + posy] = make_float2((float)(tr * norm), (float)(ti * norm));
 }
+
+// per-entry form with run-time kernel size and scale (scales above kFastMaxScale take the slow form)
+__host__ __device__ inline void transfer_entry(const TransferParams& T, int c, int posy, int posx) {
+  transfer_entry_t<0, 0>(T, c, posy, posx);
+}
+
+// ---- tiled form of the table build: one block = one channel x kTransferTile table columns.
+// The x half of the separable sum (tx[alias][column][a] and the box factor D_w) depends only on
+// the column, so it is computed once per block into shared memory (transfer_tile_x, one work item
+// per alias and column); each thread then owns table rows (posy), keeps its y phasors in
+// registers and spends k complex multiply-adds per alias pair and entry (transfer_tile_y).
+// Same arithmetic as transfer_entry_t, same fp64, same table layout.
+constexpr int kTransferTile = 32;
+struct TransferTileSmem {
+  double txr[kFastMaxScale][kTransferTile][kMaxTaps];
+  double txi[kFastMaxScale][kTransferTile][kMaxTaps];
+  double dwr[kFastMaxScale][kTransferTile], dwi[kFastMaxScale][kTransferTile];
+};
+
+template <int CK, int CS>
+__host__ __device__ inline void transfer_tile_x(const TransferParams& T, int c, int x0, int item,
+                                                TransferTileSmem& S) {
+  const int s = CS ? CS : T.s, k = CK ? CK : T.k, w = T.w, cc = k / 2;
+  const int ib = item / kTransferTile, xi = item % kTransferTile;
+  if (ib >= s || x0 + xi >= w) return;
+  const int Nw = s * w;
+  const int V = pos_to_freq(T.px, x0 + xi) + ib * w;
+  const float* K = T.weight + (size_t)c * k * k;
+  double er, ei, pr, pi;
+  cis_neg(V, Nw, er, ei);
+  const long long m0 = (long long)(-cc) * V % Nw;
+  cis_neg(m0 < 0 ? m0 + Nw : m0, Nw, pr, pi);  // ex^(-c)
+  constexpr int AK = CK ? CK : kMaxTaps;
+  double ar[AK], ai[AK];
+#pragma unroll
+  for (int a = 0; a < (CK ? CK : k); ++a) { ar[a] = 0.0; ai[a] = 0.0; }
+#pragma unroll
+  for (int b = 0; b < (CK ? CK : k); ++b) {
+#pragma unroll
+    for (int a = 0; a < (CK ? CK : k); ++a) {
+      const double kv = (double)K[a * k + b];
+      ar[a] += kv * pr;
+      ai[a] += kv * pi;
+    }
+    const double nr = pr * er - pi * ei, ni = pr * ei + pi * er;
+    pr = nr; pi = ni;
+  }
+#pragma unroll
+  for (int a = 0; a < (CK ? CK : k); ++a) { S.txr[ib][xi][a] = ar[a]; S.txi[ib][xi][a] = ai[a]; }
+  double sr = 0.0, si = 0.0, qr = 1.0, qi = 0.0;  // D_w = sum_{b<s} ex^b
+  for (int b = 0; b < s; ++b) {
+    sr += qr; si += qi;
+    const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
+    qr = nr; qi = ni;
+  }
+  S.dwr[ib][xi] = sr; S.dwi[ib][xi] = si;
+}
+
+template <int CK, int CS>
+__host__ __device__ inline void transfer_tile_y(const TransferParams& T, int c, int x0, int posy,
+                                                const TransferTileSmem& S) {
+  const int s = CS ? CS : T.s, k = CK ? CK : T.k, h = T.h, w = T.w, cc = k / 2;
+  const int Nh = s * h;
+  const int u = pos_to_freq(T.py, posy);
+  const double lam = 1.0 / (1.0 + exp(-((double)T.bias[c] - 9.0))) + (double)T.eps;
+  constexpr int AS = CS ? CS : kFastMaxScale, AK = CK ? CK : kMaxTaps;
+  double pr[AS][AK], pi[AS][AK], dhr[AS], dhi[AS];  // ey^(a-c) per alias, and D_h
+#pragma unroll
+  for (int ia = 0; ia < (CS ? CS : s); ++ia) {
+    const int U = u + ia * h;
+    double er, ei, qr, qi;
+    cis_neg(U, Nh, er, ei);
+    const long long m0 = (long long)(-cc) * U % Nh;
+    cis_neg(m0 < 0 ? m0 + Nh : m0, Nh, qr, qi);
+#pragma unroll
+    for (int a = 0; a < (CK ? CK : k); ++a) {
+      pr[ia][a] = qr; pi[ia][a] = qi;
+      const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
+      qr = nr; qi = ni;
+    }
+    double sr = 0.0, si = 0.0;
+    qr = 1.0; qi = 0.0;
+    for (int a = 0; a < s; ++a) {
+      sr += qr; si += qi;
+      const double nr = qr * er - qi * ei, ni = qr * ei + qi * er;
+      qr = nr; qi = ni;
+    }
+    dhr[ia] = sr; dhi[ia] = si;
+  }
+  const double inv_alias = 1.0 / (double)(s * s);
+  const double norm = 1.0 / ((double)h * (double)w);
+  const int nx = (w - x0 < kTransferTile) ? w - x0 : kTransferTile;
+  for (int xi = 0; xi < nx; ++xi) {
+    double num_r = 0.0, num_i = 0.0, den = 0.0;
+#pragma unroll
+    for (int ia = 0; ia < (CS ? CS : s); ++ia) {
+#pragma unroll
+      for (int ib = 0; ib < (CS ? CS : s); ++ib) {
+        double fr = 0.0, fi = 0.0;
+#pragma unroll
+        for (int a = 0; a < (CK ? CK : k); ++a) {
+          const double tr = S.txr[ib][xi][a], ti = S.txi[ib][xi][a];
+          fr += pr[ia][a] * tr - pi[ia][a] * ti;
+          fi += pr[ia][a] * ti + pi[ia][a] * tr;
+        }
+        den += fr * fr + fi * fi;
+        if (s == 1) {
+          num_r = fr; num_i = -fi;  // conj(FK)
+        } else {
+          const double dr = dhr[ia] * S.dwr[ib][xi] - dhi[ia] * S.dwi[ib][xi];
+          const double di = dhr[ia] * S.dwi[ib][xi] + dhi[ia] * S.dwr[ib][xi];
+          num_r += fr * dr - fi * di;
+          num_i += fr * di + fi * dr;
+        }
+      }
+    }
+    double tr, ti;
+    if (s == 1) {
+      const double d = den + lam;
+      tr = (num_r + lam) / d;
+      ti = num_i / d;
+    } else {
+      const double d = den * inv_alias + lam;
+      tr = (1.0 - num_r * inv_alias) / d;
+      ti = (-num_i * inv_alias) / d;
+    }
+    T.table[((size_t)c * w + x0 + xi) * h + posy] = make_float2((float)(tr * norm), (float)(ti * norm));
+  }
+}
+
+
+template <int CK, int CS>
+__host__ __device__ inline void transfer_tile_items(const TransferParams& T, int c, int x0, int tid,
+                                                    int nthreads, TransferTileSmem& S) {
+  const int s = CS ? CS : T.s;
+  for (int item = tid; item < s * kTransferTile; item += nthreads) transfer_tile_x<CK, CS>(T, c, x0, item, S);
+}
+template <int CK, int CS>
+__host__ __device__ inline void transfer_tile_rows(const TransferParams& T, int c, int x0, int tid,
+                                                   int nthreads, const TransferTileSmem& S) {
+  for (int posy = tid; posy < T.h; posy += nthreads) transfer_tile_y<CK, CS>(T, c, x0, posy, S);
+}
+
+// One block of the tiled build (block index -> channel, column tile); the host emulation calls it
+// with any thread count.
+template <int CK, int CS>
+__host__ __device__ inline void transfer_tile_block(const TransferParams& T, long long block, int nthr_emu,
+                                                    TransferTileSmem& S) {
+  (void)nthr_emu;
+  const int xtiles = (T.w + kTransferTile - 1) / kTransferTile;
+  const int c = (int)(block / xtiles), x0 = (int)(block % xtiles) * kTransferTile;
+  CVB_PHASE((transfer_tile_items<CK, CS>(T, c, x0, tid, nthr, S)));
+  CVB_PHASE((transfer_tile_rows<CK, CS>(T, c, x0, tid, nthr, S)));
+}
+
+// (kernel size, scale) pairs with a compile-time instance of the tiled build; X(k, s)
+#define CVB_TRANSFER_CASES(X) X(7, 1) X(7, 2) X(7, 4) X(5, 1) X(5, 2) X(3, 1) X(3, 2) X(2, 2)
 
 __host__ __device__ inline void twiddle_entry(const TransferParams& T, int i) {
   // tw[n] = (cos, sin)(2 pi n / N); first h entries for the column length, then w

@@ -96,20 +96,33 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
     // ================= producers =================
     const int q = lane >> 2, cg = lane & 3;
     long long chunk = 0;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    // the loads of the NEXT chunk are issued before the current one is normalised and staged, so that
+    // two chunks of global reads are in flight per producer thread
+    auto load_chunk = [&](long long tile, int kc, float4 (&dst)[16]) {
       const long long pix0 = tile * kT2Tile;
       const int b = (int)(pix0 / P.HW);
       const int p0 = (int)(pix0 - (long long)b * P.HW);
       const float* src = (const float*)(MODE == 0 ? P.x : P.t) + (size_t)b * K * P.HW + p0 + warp * 32 + q * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          dst[4 * j + e] = *(const float4*)(src + (size_t)(kc * kT2Chunk + 4 * (cg + 4 * j) + e) * P.HW);
+    };
+    float4 vn[16];
+    if ((long long)blockIdx.x < ntiles) load_chunk(blockIdx.x, 0, vn);
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
 #pragma unroll 1
       for (int kc = 0; kc < CPT; ++kc, ++chunk) {
         const int st = (int)(chunk & 1);
         float4 v[16];  // v[4*j + e] = channel 64*kc + 4*(cg+4j)+e, pixels 4q..4q+3
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            v[4 * j + e] = *(const float4*)(src + (size_t)(kc * kT2Chunk + 4 * (cg + 4 * j) + e) * P.HW);
+        for (int j = 0; j < 16; ++j) v[j] = vn[j];
+        {
+          const bool last_kc = (kc + 1 == CPT);
+          const long long ntile = last_kc ? tile + gridDim.x : tile;
+          if (ntile < ntiles) load_chunk(ntile, last_kc ? 0 : kc + 1, vn);
+        }
         float rstd[4] = {1.f, 1.f, 1.f, 1.f};
         if (MODE == 0) {
           float4 s = make_float4(0.f, 0.f, 0.f, 0.f);

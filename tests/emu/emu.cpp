@@ -35,9 +35,23 @@ int emu_build_transfer(const float* weight, const float* bias, int C, int k, int
   if (!make_plan(h, T.py) || !make_plan(w, T.px)) return -3;
   T.weight = weight; T.bias = bias; T.table = (float2*)table;
   T.C = C; T.k = k; T.s = s; T.h = h; T.w = w; T.eps = eps;
-  for (int c = 0; c < C; ++c)
-    for (int px = 0; px < w; ++px)
-      for (int py = 0; py < h; ++py) transfer_entry(T, c, py, px);
+  if (s <= kFastMaxScale) {
+    // tiled build, as the CUDA library launches it
+    static TransferTileSmem S;
+    const long long nblk = (long long)C * ((w + kTransferTile - 1) / kTransferTile);
+    for (long long blk = 0; blk < nblk; ++blk) {
+      switch (k * 10 + s) {
+#define X(KK, SS) case KK * 10 + SS: transfer_tile_block<KK, SS>(T, blk, 64, S); break;
+        CVB_TRANSFER_CASES(X)
+#undef X
+        default: transfer_tile_block<0, 0>(T, blk, 64, S); break;
+      }
+    }
+  } else {
+    for (int c = 0; c < C; ++c)
+      for (int px = 0; px < w; ++px)
+        for (int py = 0; py < h; ++py) transfer_entry(T, c, py, px);
+  }
   for (int i = 0; i < h + w; ++i) twiddle_entry(T, i);
   rader_both(T.py, T.px, T.ry, T.rx);
   for (int i = 0; T.ry.R && i < T.ry.R - 1; ++i) rader_entry(T, T.ry, i);
