@@ -14,6 +14,7 @@ int cuda_fail(cudaError_t e);
   } while (0)
 
 int env_int(const char* name, int dflt);
+int sm_count();  // multiprocessors of the current device
 
 // Number of (channel, batch-pair) work items = blocks of the shared-memory kernels.
 inline int num_pairs(const FwdParams& P) { return P.C * ((P.B + 1) / 2); }
@@ -41,9 +42,11 @@ int launch_pw_res_tc2(const BlockParams& P, int sms, int* status, cudaStream_t s
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;
 typedef int (*Strip2Launcher)(const StripParams& SP, int io_dtype, cudaStream_t st);
+typedef int (*Strip2Resident)(int io_dtype, int k, int* blocks_per_sm);  // [3]: kernels A, B, C
 struct Strip2Entry {
   int r0, r1, s0, s1;  // axis length r0 * r1; Rader sub-plan s0 * s1 of r0 - 1 (0, 0 if r0 is a register radix)
   Strip2Launcher A, B, C;
+  Strip2Resident Q;
 };
 
 // Compile-time-plan kernels (k_static.cu, one object per registry line).

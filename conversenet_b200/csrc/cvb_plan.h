@@ -133,6 +133,29 @@ inline size_t strip_smem_row(int w, int rh, bool big) {
   return ((size_t)(big ? 2 : 1) * rh * (w | 1) + w + (big ? 3 * kMaxBigPrime : 0)) * sizeof(float2);
 }
 
+// Pairs per launch of the three multi-pass kernels.  Kernel i runs (pairs * n[i]) blocks, bpsm[i]
+// of them resident per SM, so it takes ceil(blocks / (bpsm[i] * sms)) waves, each costing about
+// bpsm[i] block times on an issue-bound SM.  Among the chunk sizes between half the cap and the
+// cap this returns the cheapest in total (the largest on a tie), so that launches do not end on
+// a nearly empty wave.
+inline int balance_chunk(int npairs, int cap, const int n[3], const int bpsm[3], int sms) {
+  if (cap <= 1 || sms < 1) return cap;
+  long best_cost = -1;
+  int best = cap;
+  for (int c2 = cap; c2 >= (cap + 1) / 2; --c2) {
+    long cost = 0;
+    for (int p0 = 0; p0 < npairs; p0 += c2) {
+      const long np = (npairs - p0) < c2 ? (npairs - p0) : c2;
+      for (int i = 0; i < 3; ++i) {
+        const long slots = (long)(bpsm[i] > 0 ? bpsm[i] : 1) * sms;
+        cost += ((np * n[i] + slots - 1) / slots) * (bpsm[i] > 0 ? bpsm[i] : 1);
+      }
+    }
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c2; }
+  }
+  return best;
+}
+
 inline StripGeo strip_geometry(int h, int w, int k, int s, int npairs, size_t ws_cap = kWorkspaceTarget,
                                bool at_least_one = true) {
   StripGeo g;

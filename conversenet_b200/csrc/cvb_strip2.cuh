@@ -155,40 +155,50 @@ CVB_HD PassArgs strip_pass(float2* tile, int tp, int nlines, int N, int L, int M
   return a;
 }
 
-// tile[r][c] <-> S^T[(xfirst + c) mod w][r], lanes along r (contiguous in S^T, stride tp in the tile)
-CVB_HD void tileT_from_ws(int tid, int nthr, float2* tile, int tp, int h, int nc, const float2* ST, int w,
-                          int xfirst) {
-  const float inv_h = 1.0f / (float)h;
-  const int total = h * nc;
-  for (int i0 = tid; i0 < total; i0 += nthr * kTileUnroll) {
-    float2 v[kTileUnroll];
-    int dst[kTileUnroll];
+// tile[r][c] <-> S^T[(xfirst + c) mod w][r].  A warp takes one column c at a time with its lanes
+// along r (contiguous in S^T, odd stride tp in the tile), so no index is divided; all loads of a
+// column are issued before the first store.
+template <int H>
+CVB_HD void tileT_from_ws(int tid, int nthr, float2* tile, int tp, int nc, const float2* ST, int w, int xfirst) {
+  constexpr int U = (H + 31) / 32;
+  const int nwarps = nthr >= 32 ? nthr / 32 : 1, lanes = nthr >= 32 ? 32 : nthr;
+  const int warp = tid / lanes, lane = tid % lanes;
+  if (warp >= nwarps) return;
+  for (int c = warp; c < nc; c += nwarps) {
+    int x = xfirst + c;
+    if (x < 0) x += w;
+    if (x >= w) x -= w;
+    const float2* src = ST + (size_t)x * H;
+    for (int r0 = lane; r0 < 32; r0 += lanes) {  // one trip on the GPU; covers short emulated warps
+      float2 v[U];
 #pragma unroll
-    for (int u = 0; u < kTileUnroll; ++u) {
-      const int i = i0 + u * nthr;
-      dst[u] = -1;
-      v[u] = make_float2(0.f, 0.f);
-      if (i < total) {
-        int c, r;
-        divmod_small(i, h, inv_h, c, r);
-        int x = xfirst + c;
-        if (x < 0) x += w;
-        if (x >= w) x -= w;
-        dst[u] = r * tp + c;
-        v[u] = ST[(size_t)x * h + r];
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + 32 * u;
+        v[u] = (r < H) ? src[r] : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + 32 * u;
+        if (r < H) tile[r * tp + c] = v[u];
       }
     }
-#pragma unroll
-    for (int u = 0; u < kTileUnroll; ++u)
-      if (dst[u] >= 0) tile[dst[u]] = v[u];
   }
 }
-CVB_HD void tileT_to_ws(int tid, int nthr, const float2* tile, int tp, int h, int nc, float2* ST, int xfirst) {
-  const float inv_h = 1.0f / (float)h;
-  for (int i = tid; i < h * nc; i += nthr) {
-    int c, r;
-    divmod_small(i, h, inv_h, c, r);
-    ST[(size_t)(xfirst + c) * h + r] = tile[r * tp + c];
+template <int H>
+CVB_HD void tileT_to_ws(int tid, int nthr, const float2* tile, int tp, int nc, float2* ST, int xfirst) {
+  constexpr int U = (H + 31) / 32;
+  const int nwarps = nthr >= 32 ? nthr / 32 : 1, lanes = nthr >= 32 ? 32 : nthr;
+  const int warp = tid / lanes, lane = tid % lanes;
+  if (warp >= nwarps) return;
+  for (int c = warp; c < nc; c += nwarps) {
+    float2* dst = ST + (size_t)(xfirst + c) * H;
+    for (int r0 = lane; r0 < 32; r0 += lanes) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + 32 * u;
+        if (r < H) dst[r] = tile[r * tp + c];
+      }
+    }
   }
 }
 // tile[x][c] <-> S^T[x][y0 + c], lanes along c
@@ -291,7 +301,7 @@ __host__ __device__ void strip2_A_body(const StripParams& SP, int lp, int strip,
     CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, false, 1.0f);
   }
   CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
-  CVB_PHASE(tileT_to_ws(tid, nthr, m.cur, tp, h, nc, ST, x0));
+  CVB_PHASE(tileT_to_ws<h>(tid, nthr, m.cur, tp, nc, ST, x0));
 }
 
 // ---- B: strip of pos_y values, row transform both ways with the transfer multiply ----
@@ -363,7 +373,7 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
   CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
              copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, big ? rader_floats2(R0) : 0),
              copy_floats(tid, nthr, m.wk, gw, P.s > 1 ? P.k * P.k : 0),
-             tileT_from_ws(tid, nthr, m.cur, tp, h, nt, ST, w, x0 - hl)));
+             tileT_from_ws<h>(tid, nthr, m.cur, tp, nt, ST, w, x0 - hl)));
   CVB_PHASE((fft_pass<R1, float, h, R1, 1, 0, PASS_PRE>(tid, nthr, a1, io, 0)));
   if constexpr (!big) {
     if (P.s == 1) {

@@ -37,7 +37,37 @@ int launch_k(K kernel, const StripParams& SP, int nstrips, size_t smem, cudaStre
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
+template <typename K>
+int resident_blocks(K kernel, size_t smem) {
+  int n = 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kStrip2Threads, smem) != cudaSuccess || n < 1) {
+    (void)cudaGetLastError();
+    n = 2;
+  }
+  return n;
+}
 }  // namespace
+
+// blocks of kernels A, B, C that one SM holds at a time (asked once per element type and tap count)
+int CVB_CAT(Q, CVB_R0, CVB_R1)(int io_dtype, int k, int* bpsm) {
+  static int key = -1, cached[3] = {2, 2, 2};
+  const int want = io_dtype * 64 + k;
+  if (key != want) {
+    const size_t smem = strip2_smem(CVB_R0 * CVB_R1, kLines, CVB_R0, k);
+    if (io_dtype == CVB_F32) {
+      cached[0] = resident_blocks(strip2_A_kernel<float, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, smem);
+      cached[2] = resident_blocks(strip2_C_kernel<float, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, smem);
+    } else {
+      cached[0] = resident_blocks(strip2_A_kernel<__nv_bfloat16, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, smem);
+      cached[2] = resident_blocks(strip2_C_kernel<__nv_bfloat16, CVB_R0, CVB_R1, CVB_S0, CVB_S1>, smem);
+    }
+    cached[1] = resident_blocks(strip2_B_kernel<CVB_R0, CVB_R1, CVB_S0, CVB_S1>, smem);
+    key = want;
+  }
+  bpsm[0] = cached[0]; bpsm[1] = cached[1]; bpsm[2] = cached[2];
+  return CVB_OK;
+}
 
 int CVB_CAT(A, CVB_R0, CVB_R1)(const StripParams& SP, int io_dtype, cudaStream_t st) {
   const size_t smem = strip2_smem(CVB_R0 * CVB_R1, kLines, CVB_R0, SP.f.k);
