@@ -14,139 +14,26 @@
 //                     store (s == 1), or tile + upsampling epilogue (s > 1)
 #pragma once
 #include "cvb_strip.cuh"
+#include "cvb_tcdft.cuh"
 
 namespace cvb {
 
-constexpr int kStrip2Threads = 256;
+// Threads per block: a first radix that is a large prime runs on the tensor cores (cvb_tcdft.cuh)
+// with one block of 512 threads per SM; the register-radix plans run two blocks of 256.
+CVB_HD constexpr int strip2_threads(int R0) { return R0 > kMaxRegisterRadix ? 512 : 256; }
 // lines per strip (columns for A / C, pos_y values for B): the widest of 32 / 16 / 8 whose
-// tile(s) stay under ~76 KB, so that three blocks share an SM
+// tile stays under ~76 KB, so that three blocks share an SM; 32 (whole accumulator tiles of 128
+// vectors) for the tensor-core plans
 CVB_HD constexpr int strip2_lines(int N, int R0) {
-  const int nb = R0 > 26 ? 2 : 1;
-  return nb * N * 33 * 8 <= 76 * 1024 ? 32 : nb * N * 17 * 8 <= 76 * 1024 ? 16 : 8;
+  return R0 > kMaxRegisterRadix ? 32 : N * 33 * 8 <= 76 * 1024 ? 32 : N * 17 * 8 <= 76 * 1024 ? 16 : 8;
 }
 
-// shared memory (bytes) of one block: tile(s), twiddles, Rader tables, maps / taps
+// shared memory (bytes) of one block: tile, twiddles, maps / taps, tensor-core operands
 CVB_HD size_t strip2_smem(int N, int lines, int R0, int k) {
   const bool big = R0 > kMaxRegisterRadix;
-  const size_t f2 = (size_t)(big ? 2 : 1) * N * (lines | 1) + N + (big ? rader_floats2(R0) : 0) +
-                    (N + lines + 1) / 2 + (k * k + 1) / 2;
-  return f2 * sizeof(float2);
+  const size_t f2 = (size_t)N * (lines | 1) + N + (N + lines + 1) / 2 + (k * k + 1) / 2;
+  return f2 * sizeof(float2) + (big ? tcdft::bytes(R0) + 128 : 0);
 }
-
-// ---- Rader stage with a compile-time sub-plan R - 1 = S0 * S1, gather and scatter fused ----
-// Three phases: (1) X_0 by a direct sum + first sub-stage reading its inputs through the g^q
-// permutation straight from the tile; (2) second sub-stage with the B-hat multiply and its inverse
-// (fft_pass, PASS_MID); (3) inverse first sub-stage writing x_0 + conj(c_m) through the g^-m permutation
-// back into the tile.  `oth` holds the length-(R-1) sequences (element p = e + 1) and x_0 at p = 0.
-template <int CM>
-CVB_HD void rader_dc_fused(int tid, int nthr, float2* cur, float2* oth, const PassArgs& a, int R, bool pre,
-                           float osign) {
-  const int total = a.nlines * CM;
-  const float inv_nl = 1.0f / (float)a.nlines;
-  for (int wi = tid; wi < total; wi += nthr) {
-    int j, line;
-    divmod_small(wi, a.nlines, inv_nl, j, line);
-    float2* ip = cur + line * a.ls + j * a.es;
-    const float2 x0 = ip[0];
-    float sr = x0.x, si = x0.y;
-    for (int p = 1; p < R; ++p) {
-      float2 v = ip[p * CM * a.es];
-      if (pre && j != 0) {
-        const float2 wv = a.tw[j * p * a.tws];
-        v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
-      }
-      sr += v.x; si += v.y;
-    }
-    oth[line * a.ls + j * a.es] = x0;
-    ip[0] = make_float2(sr, osign * si);
-  }
-}
-
-template <int S0, int S1, int CM>
-CVB_HD void rader_first_pass(int tid, int nthr, const float2* cur, float2* oth, const PassArgs& a, int R,
-                             const RaderSmem& rs, bool pre) {
-  const int total = a.nlines * CM * S1;
-  const float inv_nl = 1.0f / (float)a.nlines;
-  for (int wi = tid; wi < total; wi += nthr) {
-    int rest, line;
-    divmod_small(wi, a.nlines, inv_nl, rest, line);
-    const int jp = rest / CM, jj = rest - jp * CM;   // butterfly of the sub-transform, outer j
-    const float2* bc = cur + line * a.ls + jj * a.es;
-    float2* bo = oth + line * a.ls + (jj + CM) * a.es;
-    float re[S0], im[S0];
-#pragma unroll
-    for (int q = 0; q < S0; ++q) {
-      const int p = rs.perm_in[jp + S1 * q];
-      float2 v = bc[p * CM * a.es];
-      if (pre && jj != 0) {
-        const float2 wv = a.tw[jj * p * a.tws];
-        v = make_float2(fmaf(v.y, wv.y, v.x * wv.x), fmaf(-v.x, wv.y, v.y * wv.x));
-      }
-      re[q] = v.x; im[q] = v.y;
-    }
-    Radix<S0>::fwd(re, im);
-#pragma unroll
-    for (int q = 1; q < S0; ++q) {
-      const float2 wv = rs.tw[jp * q];
-      const float xr = re[q], xi = im[q];
-      re[q] = fmaf(xi, wv.y, xr * wv.x);
-      im[q] = fmaf(-xr, wv.y, xi * wv.x);
-    }
-#pragma unroll
-    for (int q = 0; q < S0; ++q) bo[(jp + S1 * q) * CM * a.es] = make_float2(re[q], im[q]);
-  }
-}
-
-template <int S0, int S1, int CM>
-CVB_HD void rader_last_pass(int tid, int nthr, float2* cur, const float2* oth, const PassArgs& a, int R,
-                            const RaderSmem& rs, bool post, float osign) {
-  const int total = a.nlines * CM * S1;
-  const float inv_nl = 1.0f / (float)a.nlines;
-  for (int wi = tid; wi < total; wi += nthr) {
-    int rest, line;
-    divmod_small(wi, a.nlines, inv_nl, rest, line);
-    const int jp = rest / CM, jj = rest - jp * CM;
-    const float2* bo = oth + line * a.ls + (jj + CM) * a.es;
-    float2* bc = cur + line * a.ls + jj * a.es;
-    const float2 x0 = oth[line * a.ls + jj * a.es];
-    float re[S0], im[S0];
-#pragma unroll
-    for (int q = 0; q < S0; ++q) {
-      const float2 v = bo[(jp + S1 * q) * CM * a.es];
-      re[q] = v.x; im[q] = v.y;
-    }
-#pragma unroll
-    for (int q = 1; q < S0; ++q) {
-      const float2 wv = rs.tw[jp * q];
-      const float xr = re[q], xi = im[q];
-      re[q] = fmaf(xi, wv.y, xr * wv.x);
-      im[q] = fmaf(-xr, wv.y, xi * wv.x);
-    }
-    Radix<S0>::fwd(re, im);
-#pragma unroll
-    for (int q = 0; q < S0; ++q) {
-      const int k = rs.perm_out[jp + S1 * q];
-      float vr = x0.x + re[q], vi = x0.y - im[q];   // x_0 + conj(c_m)
-      if (post && jj != 0) {
-        const float2 wv = a.tw[jj * k * a.tws];
-        const float tr = fmaf(vi, wv.y, vr * wv.x), ti = fmaf(-vr, wv.y, vi * wv.x);
-        vr = tr; vi = ti;
-      }
-      bc[k * CM * a.es] = make_float2(vr, osign * vi);
-    }
-  }
-}
-
-#define CVB_RADER_STATIC(R, R1_, S0, S1, cur, oth, a_, rinfo, rsm, pre_, osg_)                              \
-  do {                                                                                                    \
-    CVB_PHASE((rader_dc_fused<R1_>(tid, nthr, cur, oth, a_, R, pre_, osg_),                               \
-               rader_first_pass<S0, S1, R1_>(tid, nthr, cur, oth, a_, R, rsm, pre_)));                    \
-    {                                                                                                     \
-      const PassArgs s_ = rader_sub_pass(oth, a_, rinfo, 1, rsm);                                         \
-      CVB_PHASE((fft_pass<S1, float, R - 1, S1, 1, 0, PASS_MID>(tid, nthr, s_, io, 0)));                  \
-    }                                                                                                     \
-    CVB_PHASE((rader_last_pass<S0, S1, R1_>(tid, nthr, cur, oth, a_, R, rsm, !(pre_), osg_)));            \
-  } while (0)
 
 CVB_HD PassArgs strip_pass(float2* tile, int tp, int nlines, int N, int L, int M, const float2* tw) {
   PassArgs a = make_pass(tile, true, tp, 0, 0, N, L, M, tw);
@@ -248,26 +135,27 @@ CVB_HD void strip_maps(int tid, int nthr, int* rmap, int* cmap, int x0, int nc, 
 // carve one block's shared memory
 struct Strip2Smem {
   float2* cur;
-  float2* oth;
   float2* tw;
-  float2* rtab;
   int* rmap;
   int* cmap;
   float* wk;
+  void* tc;   // tensor-core operands of a large-prime plan (128-byte aligned)
 };
-CVB_HD Strip2Smem strip2_carve(float2* smem, int N, int lines, int R0) {
-  const bool big = R0 > kMaxRegisterRadix;
+CVB_HD Strip2Smem strip2_carve(float2* smem, int N, int lines, int k) {
   const int tp = lines | 1;
   Strip2Smem m;
   m.cur = smem;
-  m.oth = big ? smem + N * tp : smem;
-  m.tw = m.oth + N * tp;
-  m.rtab = m.tw + N;
-  m.rmap = (int*)(m.rtab + (big ? rader_floats2(R0) : 0));
+  m.tw = m.cur + N * tp;
+  m.rmap = (int*)(m.tw + N);
   m.cmap = m.rmap + N;
   m.wk = (float*)((float2*)m.rmap + (N + lines + 1) / 2);
+  m.tc = (void*)(((uintptr_t)(m.wk + 2 * ((k * k + 1) / 2)) + 127) & ~(uintptr_t)127);
   return m;
 }
+
+// one large-prime stage over the whole tile (all threads on the GPU; plain loops on the host)
+#define CVB_TC_STAGE(R, R1_, LN_, ctx, cur, tp, tw, pre_, osg_) \
+  tcdft::stage<R, R1_, LN_>(ctx, cur, tp, tw, pre_, osg_, nthr_emu)
 
 // ---- A: column strip forward ----
 template <typename IO, int R0, int R1, int S0, int S1>
@@ -281,9 +169,8 @@ __host__ __device__ void strip2_A_body(const StripParams& SP, int lp, int strip,
   const int x0 = strip * LN;
   const int nc = (w - x0) < LN ? (w - x0) : LN;
   constexpr int tp = LN | 1;
-  Strip2Smem m = strip2_carve(smem, h, LN, R0);
+  Strip2Smem m = strip2_carve(smem, h, LN, P.k);
   const float2* blob = P.table + (size_t)P.C * h * w;
-  const RaderSmem rsm = rader_views(m.rtab, big ? R0 : 1);
   int c;
   IoArgs io = strip_io<IO>(P, SP.pair0 + lp, c);
   io.rmap = m.rmap;
@@ -295,10 +182,14 @@ __host__ __device__ void strip2_A_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h), strip_maps(tid, nthr, m.rmap, m.cmap, x0, nc, P)));
     CVB_PHASE((fft_pass<R0, IO, h, h, R1, 0, PASS_SRC_GLOBAL>(tid, nthr, a0, io, 0)));
   } else {
-    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
-               copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, rader_floats2(R0)),
-               tile_load_x<IO>(tid, nthr, m.cur, tp, nc, x0, P, io)));
-    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, false, 1.0f);
+    tcdft::Ctx tcx = tcdft::carve<R0>(m.tc, P.status);
+    tcdft::setup<R0>(tcx);
+    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h), tile_load_x<IO>(tid, nthr, m.cur, tp, nc, x0, P, io)));
+    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, false, 1.0f);
+    CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
+    CVB_PHASE(tileT_to_ws<h>(tid, nthr, m.cur, tp, nc, ST, x0));
+    tcdft::finish(tcx);
+    return;
   }
   CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
   CVB_PHASE(tileT_to_ws<h>(tid, nthr, m.cur, tp, nc, ST, x0));
@@ -316,9 +207,8 @@ __host__ __device__ void strip2_B_body(const StripParams& SP, int lp, int strip,
   const int y0 = strip * LN;
   const int nc = (h - y0) < LN ? (h - y0) : LN;
   constexpr int tp = LN | 1;
-  Strip2Smem m = strip2_carve(smem, w, LN, R0);
+  Strip2Smem m = strip2_carve(smem, w, LN, P.k);
   const float2* blob = P.table + (size_t)P.C * h * w;
-  const RaderSmem rsm = rader_views(m.rtab, big ? R0 : 1);
   int c;
   IoArgs io = strip_io<float>(P, SP.pair0 + lp, c);
   float2* ST = SP.ws + (size_t)lp * h * w;
@@ -335,13 +225,14 @@ __host__ __device__ void strip2_B_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
     CVB_PHASE((fft_pass<R0, float, w, w, R1, 0, PASS_PRE | PASS_DST_WS>(tid, nthr, a0, io, 0)));
   } else {
-    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob + h, w),
-               copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.rx.off, rader_floats2(R0)),
-               tile_rows_from_ws(tid, nthr, m.cur, tp, w, nc, ST, h, y0)));
-    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, false, 1.0f);
+    tcdft::Ctx tcx = tcdft::carve<R0>(m.tc, P.status);
+    tcdft::setup<R0>(tcx);
+    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob + h, w), tile_rows_from_ws(tid, nthr, m.cur, tp, w, nc, ST, h, y0)));
+    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, false, 1.0f);
     CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
-    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, true, 1.0f);
+    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, true, 1.0f);
     CVB_PHASE(tile_rows_to_ws(tid, nthr, m.cur, tp, w, nc, ST, h, y0));
+    tcdft::finish(tcx);
   }
 }
 
@@ -360,9 +251,8 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
   const int nc = (w - x0) < cw ? (w - x0) : cw;
   const int nt = nc + hl + hr;
   constexpr int tp = LN | 1;
-  Strip2Smem m = strip2_carve(smem, h, LN, R0);
+  Strip2Smem m = strip2_carve(smem, h, LN, P.k);
   const float2* blob = P.table + (size_t)P.C * h * w;
-  const RaderSmem rsm = rader_views(m.rtab, big ? R0 : 1);
   int c;
   IoArgs io = strip_io<IO>(P, SP.pair0 + lp, c);
   io.xoff = x0;
@@ -370,8 +260,9 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
   const PassArgs a0 = strip_pass(m.cur, tp, nt, h, h, R1, m.tw);
   const PassArgs a1 = strip_pass(m.cur, tp, nt, h, R1, 1, m.tw);
   const float* gw = P.weight + (size_t)c * P.k * P.k;
+  tcdft::Ctx tcx = tcdft::carve<big ? R0 : 3>(m.tc, P.status);
+  if constexpr (big) tcdft::setup<R0>(tcx);
   CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
-             copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, big ? rader_floats2(R0) : 0),
              copy_floats(tid, nthr, m.wk, gw, P.s > 1 ? P.k * P.k : 0),
              tileT_from_ws<h>(tid, nthr, m.cur, tp, nt, ST, w, x0 - hl)));
   CVB_PHASE((fft_pass<R1, float, h, R1, 1, 0, PASS_PRE>(tid, nthr, a1, io, 0)));
@@ -383,12 +274,13 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
       CVB_PHASE(tile_epilogue<IO>(tid, nthr, m.cur, tp, nc, x0, hl, m.wk, P, io));
     }
   } else {
-    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, true, -1.0f);
+    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, true, -1.0f);
     if (P.s == 1) {
       CVB_PHASE(tile_store_crop<IO>(tid, nthr, m.cur, tp, nc, x0, P, io));
     } else {
       CVB_PHASE(tile_epilogue<IO>(tid, nthr, m.cur, tp, nc, x0, hl, m.wk, P, io));
     }
+    tcdft::finish(tcx);
   }
 }
 

@@ -12,19 +12,21 @@
 namespace cvb {
 
 constexpr int kLines = strip2_lines(CVB_R0 * CVB_R1, CVB_R0);
+constexpr int kThreads = strip2_threads(CVB_R0);
+constexpr int kMinBlocks = kThreads > 256 ? 1 : 2;
 
 template <typename IO, int R0, int R1, int S0, int S1>
-__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_A_kernel(const StripParams SP) {
+__global__ void __launch_bounds__(kThreads, kMinBlocks) strip2_A_kernel(const StripParams SP) {
   extern __shared__ float2 smem[];
   strip2_A_body<IO, R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
 }
 template <int R0, int R1, int S0, int S1>
-__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_B_kernel(const StripParams SP) {
+__global__ void __launch_bounds__(kThreads, kMinBlocks) strip2_B_kernel(const StripParams SP) {
   extern __shared__ float2 smem[];
   strip2_B_body<R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
 }
 template <typename IO, int R0, int R1, int S0, int S1>
-__global__ void __launch_bounds__(kStrip2Threads, 2) strip2_C_kernel(const StripParams SP) {
+__global__ void __launch_bounds__(kThreads, kMinBlocks) strip2_C_kernel(const StripParams SP) {
   extern __shared__ float2 smem[];
   strip2_C_body<IO, R0, R1, S0, S1>(SP, blockIdx.y, blockIdx.x, smem, 0);
 }
@@ -33,7 +35,7 @@ namespace {
 template <typename K>
 int launch_k(K kernel, const StripParams& SP, int nstrips, size_t smem, cudaStream_t st) {
   CVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kernel<<<dim3(nstrips, SP.npair), kStrip2Threads, smem, st>>>(SP);
+  kernel<<<dim3(nstrips, SP.npair), kThreads, smem, st>>>(SP);
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
@@ -41,7 +43,7 @@ template <typename K>
 int resident_blocks(K kernel, size_t smem) {
   int n = 0;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kStrip2Threads, smem) != cudaSuccess || n < 1) {
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, smem) != cudaSuccess || n < 1) {
     (void)cudaGetLastError();
     n = 2;
   }
