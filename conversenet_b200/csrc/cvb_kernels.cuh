@@ -152,6 +152,23 @@ enum {
   PASS_DST_WS = 64      // write them to the workspace instead of shared memory
 };
 
+// Transfer-table values of work item wi of a PASS_MID stage (same index arithmetic as fft_pass).
+template <int R, int CN, int CL, int CM, int CNL>
+CVB_HD void mid_table_load(const PassArgs& a, const IoArgs& io, int wi, float2 (&g)[R]) {
+  int t, line;
+  if constexpr (CNL != 0) {
+    t = wi / CNL;
+    line = wi - t * CNL;
+  } else {
+    divmod_small(wi, a.nlines, a.inv_nlines, t, line);
+  }
+  const int tes = a.tab ? a.tab_es : io.h;
+  const float2* tp = a.tab ? a.tab + (t * R) * a.tab_es + line * a.tab_ls
+                           : io.tab + (size_t)(t * R) * io.h + line;
+#pragma unroll
+  for (int p = 0; p < R; ++p) g[p] = tp[(size_t)p * tes];
+}
+
 // CN, CL, CM, CNL: compile-time transform length, stage sub-length, L/R and line
 // count (0 = take the run-time value from PassArgs); strides stay run-time so that
 // the row and the column stage of a square plane share one instantiation.
@@ -165,6 +182,11 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
   const int nrep = (flags & PASS_MID) ? 2 : 1;
   const float osign = (flags & PASS_CONJ_OUT) ? -1.0f : 1.0f;
   const bool twiddle = aM > 1;
+  constexpr bool kMidStatic = CFLAGS >= 0 && (CFLAGS & PASS_MID) != 0;
+  float2 gtab[kMidStatic ? R : 1], gnext[kMidStatic ? R : 1];
+  if constexpr (kMidStatic) {
+    if (tid < total) mid_table_load<R, CN, CL, CM, CNL>(a, io, tid, gnext);
+  }
   for (int wi = tid; wi < total; wi += nthr) {
     int t, line, blk, j;
     if constexpr (CNL != 0) {
@@ -187,6 +209,14 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
     const int st = aM * a.es;
     const int tstep = j * atws;
     float re[R], im[R];
+    // transfer-table values (global memory) are fetched one work item ahead, so that their
+    // latency overlaps this item's shared-memory traffic and butterflies
+    if constexpr (kMidStatic) {
+#pragma unroll
+      for (int p = 0; p < R; ++p) gtab[p] = gnext[p];
+      const int wn = wi + nthr;
+      if (wn < total) mid_table_load<R, CN, CL, CM, CNL>(a, io, wn, gnext);
+    }
 
     if (flags & PASS_SRC_GLOBAL) {
       // rows base + q*M of padded column `line`, straight from x
@@ -244,7 +274,9 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
                                  : io.tab + (size_t)(t * R) * io.h + line;
 #pragma unroll
         for (int p = 0; p < R; ++p) {
-          const float2 g = tp[(size_t)p * tes];
+          float2 g;
+          if constexpr (kMidStatic) g = gtab[p];
+          else g = tp[(size_t)p * tes];
           const float xr = re[p], xi = im[p];
           re[p] = fmaf(-xi, g.y, xr * g.x);
           im[p] = -fmaf(xr, g.y, xi * g.x);
