@@ -64,6 +64,11 @@ LARGE = {
     "usrnet_block_516": dict(B=1, C=4, H=512, W=512, k=3, s=1, p=2, mode="circular", eps=1e-5),
     "usrnet_data_512": dict(B=2, C=2, H=512, W=512, k=7, s=1, p=0, mode="circular", eps=1e-3),
     "odd_rect_prime": dict(B=3, C=3, H=83, W=55, k=3, s=3, p=2, mode="reflect", eps=1e-5),  # 87 x 59
+    # 268 = 67 * 4: the 67-point stage on the tensor cores; with the upsampling epilogue (halo columns in
+    # the 16-line tiles, odd plane count), and mixed with a register-radix axis both ways round
+    "tc_268_up2": dict(B=3, C=3, H=264, W=264, k=3, s=2, p=2, mode="replicate", eps=1e-5),
+    "tc_268x264": dict(B=2, C=5, H=256, W=252, k=7, s=1, p=6, mode="circular", eps=1e-5),
+    "tc_264x268": dict(B=1, C=6, H=252, W=256, k=5, s=1, p=6, mode="reflect", eps=1e-5),
 }
 
 
@@ -74,6 +79,23 @@ def test_large_planes_multi_pass(name):
     out = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
     ref64 = orc.converse2d_forward(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float64)
     assert orc.rel_l2(out, ref64) <= TOL_FP32
+
+
+def test_tensor_core_stage_bf16_io_and_status_word():
+    """268-wide planes with bf16 tensors; the device status word must stay clear (no bounded wait ran out)."""
+    from conversenet_b200 import _cabi
+    lib = _cabi.load()
+    lib.cvb_last_device_status(1)
+    cfg = LARGE["dncnn_body_268"]
+    x, w, b = _seeded(cfg, 9)
+    xb = torch.from_numpy(x).bfloat16()
+    out = _run(xb.float().numpy(), w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
+    ref = orc.converse2d_forward(xb.float().numpy(), w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"],
+                                 dtype=np.float32)
+    ref = torch.from_numpy(ref).bfloat16().float().numpy()
+    assert orc.rel_l2(out, ref) <= TOL_BF16
+    torch.cuda.synchronize()
+    assert lib.cvb_last_device_status(0) == 0
 
 
 def test_forced_multi_pass_matches_shared_memory_path(monkeypatch):
