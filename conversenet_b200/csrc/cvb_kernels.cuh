@@ -414,7 +414,13 @@ CVB_HD void store_run_f32(void* base, size_t off, const float (&v)[N], bool vec,
   if constexpr (N % 4 == 0) {
     if (vec) {
 #pragma unroll
-      for (int i = 0; i < N; i += 4) *(float4*)(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      for (int i = 0; i < N; i += 4) {
+#ifdef __CUDA_ARCH__
+        __stcs((float4*)(o + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));   // written once, read by a later kernel
+#else
+        *(float4*)(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#endif
+      }
       return;
     }
   }

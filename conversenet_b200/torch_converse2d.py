@@ -8,7 +8,10 @@
 (B,C,s*h,s*w) solve, as in the reference.  The native kernels implement the solve for
 `x0 = nearest-upsample(x)`, which is what `Converse2D.forward` passes
 (`models/util_converse.py:166`); any other `x0` is refused with a RuntimeError rather
-than answered wrongly.  Forward only.
+than answered wrongly.  Differentiable as the reference's op is (CompositeImplicitAutograd there):
+dL/dx through the native kernels with `x0` tied to `x` (the gradient returned for `x0` is zero, so the
+chain through `x0 = interpolate(x)` adds nothing twice), parameter gradients through the `torch.fft`
+restatement in `conversenet_b200/autograd.py`.
 
 Do not import this module in a process that also loads the reference's own extension:
 a schema can be defined once.
@@ -71,6 +74,32 @@ def _clear_cache():
     _cache.clear()
 
 
+def _setup_context(ctx, inputs, output):
+    x, x0, weight, bias, scale, eps = inputs
+    ctx.save_for_backward(x, weight, bias)
+    ctx.cfg = (int(scale), float(eps))
+
+
+def _backward(ctx, g):
+    from .autograd import grad_input, spectral_forward
+    x, weight, bias = ctx.saved_tensors
+    scale, eps = ctx.cfg
+    gx = gw = gb = None
+    if ctx.needs_input_grad[0]:
+        gx = grad_input(g, weight, bias, scale, 0, "circular", eps, x.shape)
+    if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+        with torch.enable_grad():
+            w_ = weight.detach().float().requires_grad_(True)
+            b_ = bias.detach().float().requires_grad_(True)
+            out = spectral_forward(x.detach().float(), w_, b_, scale, 0, "circular", eps)
+            gw, gb = torch.autograd.grad(out, (w_, b_), g.float())
+        gw = gw.to(weight.dtype) if ctx.needs_input_grad[2] else None
+        gb = gb.to(bias.dtype) if ctx.needs_input_grad[3] else None
+    gx0 = torch.zeros_like(g) if ctx.needs_input_grad[1] else None
+    return gx, gx0, gw, gb, None, None
+
+
 _lib.impl("forward", _forward, "CUDA")
 _lib.impl("forward", _forward, "CPU")  # raises: no CPU path
 _lib.impl("clear_cache", _clear_cache, "CompositeExplicitAutograd")
+torch.library.register_autograd("converse2d::forward", _backward, setup_context=_setup_context, lib=_lib)

@@ -56,6 +56,9 @@ class Converse2D(nn.Module):
     `weight (1,C,k,k)` (softmax-normalised normal draw) and `bias (1,C,1,1)`
     (zeros), `forward(x: (B,C,H,W)) -> (B,C,H*scale,W*scale)`.
 
+    With autograd enabled and an input or parameter that requires a gradient the call is
+    differentiable (`conversenet_b200/autograd.py`: dL/dx through the native kernels).
+
     `backend` is accepted for compatibility: 'auto' and 'cuda' run the native
     kernels; 'pytorch' (or CONVERSE2D_BACKEND=pytorch) raises, because this build
     carries no torch.fft path.  The output is contiguous (the reference returns a
@@ -115,6 +118,12 @@ class Converse2D(nn.Module):
             raise RuntimeError("x must be (B,%d,H,W)" % self.in_channels)
         h, w = x.size(2) + 2 * self.padding, x.size(3) + 2 * self.padding
         table, wf = self._table_for(h, w, x.device)
+        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad or self.bias.requires_grad):
+            # differentiable route (the reference is differentiable through torch.fft, converse2d.cpp:223)
+            from .autograd import Converse2DFunction
+            out = Converse2DFunction.apply(x, self.weight, self.bias, table, wf, self.kernel_size, self.scale,
+                                           self.padding, self.padding_mode, self.eps)
+            return F.gelu(out) if self.fuse_gelu else out
         return CF.converse2d_forward(x, table, wf, self.kernel_size, self.scale, self.padding,
                                      self.padding_mode, fuse_gelu=self.fuse_gelu)
 
@@ -151,6 +160,8 @@ class ConverseBlock(nn.Module):
 
     def _fusable(self, x):
         c1, c2 = self.conv1, self.conv2
+        if torch.is_grad_enabled() and (x.requires_grad or any(q.requires_grad for q in self.parameters())):
+            return False  # the fused block kernels are forward-only
         return (x.is_cuda and x.dim() == 4 and x.size(1) == 64 and c1[1].out_channels == 128 and
                 c1[5].out_channels == 64 and c1[3].scale == 1 and x.dtype in (torch.float32, torch.bfloat16) and
                 c1[1].bias is not None and c1[5].bias is not None and c2[1].bias is not None and
