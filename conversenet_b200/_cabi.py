@@ -23,6 +23,8 @@ SIGNATURES = {
     "cvb_transfer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int, _c.c_int]),
     "cvb_build_transfer": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                       _c.c_int, _c.c_float, _c.c_void_p, _c.c_void_p]),
+    "cvb_build_x0_table": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                      _c.c_int, _c.c_float, _c.c_void_p, _c.c_void_p]),
     "cvb_converse2d_workspace_bytes": (_c.c_size_t, [_c.c_int] * 7),
     "cvb_converse2d_fwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p] + [_c.c_int] * 10 +
                            [_c.c_void_p, _c.c_size_t, _c.c_void_p]),

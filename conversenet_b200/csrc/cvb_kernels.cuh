@@ -969,6 +969,7 @@ struct TransferParams {
   float2* table;
   int C, k, s, h, w;
   float eps;
+  int kind;  // 0: the operator's multiplier; 1: 1 / (alias mean of |FK|^2 + lambda), the x0 term's multiplier
   Plan1D py, px;
   RaderInfo ry, rx;
 };
@@ -1027,7 +1028,10 @@ __host__ __device__ inline void transfer_entry_slow(const TransferParams& T, int
   const double inv_alias = 1.0 / (double)(s * s);
   const double norm = 1.0 / ((double)h * (double)w);
   double tr, ti;
-  if (s == 1) {
+  if (T.kind == 1) {
+    tr = 1.0 / (den * inv_alias + lam);
+    ti = 0.0;
+  } else if (s == 1) {
     const double d = den + lam;
     tr = (num_r + lam) / d;
     ti = num_i / d;
@@ -1139,7 +1143,10 @@ __host__ __device__ inline void transfer_entry_t(const TransferParams& T, int c,
   const double inv_alias = 1.0 / (double)(s * s);
   const double norm = 1.0 / ((double)h * (double)w);
   double tr, ti;
-  if (s == 1) {
+  if (T.kind == 1) {
+    tr = 1.0 / (den * inv_alias + lam);
+    ti = 0.0;
+  } else if (s == 1) {
     const double d = den + lam;
     tr = (num_r + lam) / d;
     ti = num_i / d;
@@ -1267,7 +1274,10 @@ __host__ __device__ inline void transfer_tile_y(const TransferParams& T, int c, 
       }
     }
     double tr, ti;
-    if (s == 1) {
+    if (T.kind == 1) {
+      tr = 1.0 / (den * inv_alias + lam);
+      ti = 0.0;
+    } else if (s == 1) {
       const double d = den + lam;
       tr = (num_r + lam) / d;
       ti = num_i / d;

@@ -18,8 +18,10 @@ def _io_dtype(t):
     raise RuntimeError("Converse2D supports float32 and bfloat16 tensors, got %s" % t.dtype)
 
 
-def build_transfer(weight, bias, scale, eps, h, w):
+def build_transfer(weight, bias, scale, eps, h, w, x0_term=False):
     """Transfer table for `weight` (1,C,k,k) / `bias` (1,C,1,1) at padded size h x w.
+    `x0_term`: the real table 1 / (alias mean of |FK|^2 + lambda) that the term of an
+    arbitrary `x0` needs (`cvb_build_x0_table`) instead of the operator's multiplier.
 
     Plays the role of the reference's cached kernel spectrum
     (`converse2d.cpp:58-102`), but holds the complete weights-only multiplier.
@@ -43,8 +45,9 @@ def build_transfer(weight, bias, scale, eps, h, w):
     bf = bias.detach().reshape(C).to(torch.float32).contiguous()
     table = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
     with torch.cuda.device(weight.device):
-        rc = lib.cvb_build_transfer(wf.data_ptr(), bf.data_ptr(), C, k, int(scale), h, w, float(eps),
-                                    table.data_ptr(), _stream_ptr(weight.device))
+        fn = lib.cvb_build_x0_table if x0_term else lib.cvb_build_transfer
+        rc = fn(wf.data_ptr(), bf.data_ptr(), C, k, int(scale), h, w, float(eps), table.data_ptr(),
+                _stream_ptr(weight.device))
     _cabi.check(rc, "cvb_build_transfer")
     return table, wf
 

@@ -5,10 +5,14 @@
     forward(Tensor x, Tensor x0, Tensor weight, Tensor bias, int scale, float eps=1e-5) -> Tensor
 
 `x` is the already padded plane batch (B,C,h,w), the result is the UNCROPPED
-(B,C,s*h,s*w) solve, as in the reference.  The native kernels implement the solve for
+(B,C,s*h,s*w) solve, as in the reference.  The fused kernels implement the solve for
 `x0 = nearest-upsample(x)`, which is what `Converse2D.forward` passes
-(`models/util_converse.py:166`); any other `x0` is refused with a RuntimeError rather
-than answered wrongly.  Differentiable as the reference's op is (CompositeImplicitAutograd there):
+(`models/util_converse.py:166`).  The operator is linear in (x, x0), so any other `x0` is
+answered as  solve(x, nearest(x)) + T(d),  d = x0 - nearest(x), with
+    T(d) = d - corr(K, zero_insert_s(q)),   q = IFFT2( FFT2(decimate_s(K * d)) / (alias mean |FK|^2 + lambda) )
+(`models/util_converse.py:178-187` with x = 0): the two FFTs are the forward kernel at scale 1 with the
+table of `cvb_build_x0_table`, the k x k correlations are PyTorch convolutions.
+Differentiable as the reference's op is (CompositeImplicitAutograd there):
 dL/dx through the native kernels with `x0` tied to `x` (the gradient returned for `x0` is zero, so the
 chain through `x0 = interpolate(x)` adds nothing twice), parameter gradients through the `torch.fft`
 restatement in `conversenet_b200/autograd.py`.
@@ -51,10 +55,11 @@ def _forward(x, x0, weight, bias, scale, eps=1e-5):
     if tuple(x0.shape) != (B, C, h * scale, w * scale):
         raise RuntimeError("x0 must be (B,C,scale*H,scale*W)")
     same = x0.data_ptr() == x.data_ptr() if scale == 1 else False
+    d = None
     if not same:
         ref = x if scale == 1 else F.interpolate(x, scale_factor=scale, mode="nearest")
         if not torch.equal(x0, ref):
-            raise RuntimeError("converse2d.forward: only x0 = nearest-upsample(x) is implemented natively")
+            d = (x0 - ref).float()
     key = (x.device, weight.data_ptr(), weight._version, bias.data_ptr(), bias._version, C, h, w, int(scale),
            float(eps))
     hit = _cache.get(key)
@@ -67,7 +72,29 @@ def _forward(x, x0, weight, bias, scale, eps=1e-5):
         _cache.move_to_end(key)
     table, wf = hit
     # padding 0: the solve on the plane as given, nothing cropped
-    return CF.converse2d_forward(x, table, wf, weight.size(2), int(scale), 0, "circular")
+    out = CF.converse2d_forward(x, table, wf, weight.size(2), int(scale), 0, "circular")
+    if d is not None:
+        out = out + _x0_term(d, weight, bias, wf, int(scale), float(eps), h, w).to(out.dtype)
+    return out
+
+
+def _x0_term(d, weight, bias, wf, s, eps, h, w):
+    """T(d) for d = x0 - nearest(x), (B,C,s*h,s*w) fp32."""
+    C, k = wf.size(0), wf.size(1)
+    c = k // 2
+    key = ("x0", d.device, weight.data_ptr(), weight._version, bias.data_ptr(), bias._version, C, h, w, s, eps)
+    tab = _cache.get(key)
+    if tab is None:
+        tab = CF.build_transfer(weight, bias, s, eps, h, w, x0_term=True)[0]
+        _cache[key] = tab
+    # e[m] = (K * d)[s m] = sum_a K[a] d[s m - a + c], circular
+    dp = F.pad(d, (k - 1 - c, c, k - 1 - c, c), mode="circular")
+    e = F.conv2d(dp, wf.flip(-2, -1).reshape(C, 1, k, k), stride=s, groups=C).contiguous()
+    q = CF.converse2d_forward(e, tab, wf, k, 1, 0, "circular")
+    z = torch.zeros_like(d)
+    z[..., ::s, ::s] = q
+    zp = F.pad(z, (c, k - 1 - c, c, k - 1 - c), mode="circular")
+    return d - F.conv2d(zp, wf.reshape(C, 1, k, k), groups=C)
 
 
 def _clear_cache():
@@ -78,12 +105,16 @@ def _setup_context(ctx, inputs, output):
     x, x0, weight, bias, scale, eps = inputs
     ctx.save_for_backward(x, weight, bias)
     ctx.cfg = (int(scale), float(eps))
+    ref = x if int(scale) == 1 else F.interpolate(x, scale_factor=int(scale), mode="nearest")
+    ctx.tied = bool(torch.equal(x0, ref))
 
 
 def _backward(ctx, g):
     from .autograd import grad_input, spectral_forward
     x, weight, bias = ctx.saved_tensors
     scale, eps = ctx.cfg
+    if not ctx.tied:
+        raise NotImplementedError("converse2d.forward: the backward is written for x0 = nearest-upsample(x)")
     gx = gw = gb = None
     if ctx.needs_input_grad[0]:
         gx = grad_input(g, weight, bias, scale, 0, "circular", eps, x.shape)

@@ -80,6 +80,18 @@ int cvb_build_transfer(const float* weight, const float* bias, int C, int k, int
                        float eps, void* table, void* stream);
 
 /*
+ * Table of the x0 term, same arguments and layout: the real multiplier
+ * 1 / (mean over the s x s aliases of |FK|^2 + lambda), i.e. 1 / (invW + lambda) of
+ * models/util_converse.py:183-184 (converse2d.cpp:199-201).  The raw operator
+ * (converse2d.cpp:165,193) accepts an x0 that is not the nearest-upsampled input; its
+ * extra term  d - corr(K, zero_insert(IFFT2(table . FFT2(decimate(K * d))))),
+ * d = x0 - nearest(x), runs through cvb_converse2d_fwd at scale 1 with this table
+ * (conversenet_b200/torch_converse2d.py).
+ */
+int cvb_build_x0_table(const float* weight, const float* bias, int C, int k, int s, int h, int w,
+                       float eps, void* table, void* stream);
+
+/*
  * Bytes of scratch the forward needs for this shape (0 when the plane fits in
  * shared memory and everything stays on chip).
  */

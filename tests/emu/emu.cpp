@@ -29,12 +29,12 @@ static void run_strip2(StripParams& SP, int npairs, int chunk, std::vector<float
 
 extern "C" {
 
-int emu_build_transfer(const float* weight, const float* bias, int C, int k, int s, int h, int w,
-                       float eps, void* table) {
+static int build_table(const float* weight, const float* bias, int C, int k, int s, int h, int w,
+                       float eps, void* table, int kind) {
   TransferParams T;
   if (!make_plan(h, T.py) || !make_plan(w, T.px)) return -3;
   T.weight = weight; T.bias = bias; T.table = (float2*)table;
-  T.C = C; T.k = k; T.s = s; T.h = h; T.w = w; T.eps = eps;
+  T.C = C; T.k = k; T.s = s; T.h = h; T.w = w; T.eps = eps; T.kind = kind;
   if (s <= kFastMaxScale) {
     // tiled build, as the CUDA library launches it
     static TransferTileSmem S;
@@ -57,6 +57,16 @@ int emu_build_transfer(const float* weight, const float* bias, int C, int k, int
   for (int i = 0; T.ry.R && i < T.ry.R - 1; ++i) rader_entry(T, T.ry, i);
   for (int i = 0; T.rx.R && i < T.rx.R - 1; ++i) rader_entry(T, T.rx, i);
   return 0;
+}
+
+int emu_build_transfer(const float* weight, const float* bias, int C, int k, int s, int h, int w,
+                       float eps, void* table) {
+  return build_table(weight, bias, C, k, s, h, w, eps, table, 0);
+}
+// the x0 term's table: 1 / (alias mean of |FK|^2 + lambda)
+int emu_build_x0_table(const float* weight, const float* bias, int C, int k, int s, int h, int w,
+                       float eps, void* table) {
+  return build_table(weight, bias, C, k, s, h, w, eps, table, 1);
 }
 
 // variant: 0 = runtime-plan body, 1 = compile-time-plan body (only for the sizes instantiated below)

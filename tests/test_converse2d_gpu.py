@@ -238,6 +238,24 @@ def test_registered_torch_op_matches_reference_contract(golden):
     crop = out[..., p * s:-p * s, p * s:-p * s].cpu().numpy()
     assert orc.rel_l2(crop, ref64) <= TOL_FP32
     torch.ops.converse2d.clear_cache()
-    with pytest.raises(RuntimeError):
-        torch.ops.converse2d.forward(y, torch.randn_like(x0), torch.from_numpy(w).cuda(),
+    with pytest.raises(RuntimeError):   # x0 of the wrong shape
+        torch.ops.converse2d.forward(y, x0[..., :-1], torch.from_numpy(w).cuda(),
                                      torch.from_numpy(b).cuda(), s, c["eps"])
+
+
+@pytest.mark.parametrize("shape,k,s", [((2, 3, 20, 26), 5, 2), ((1, 4, 32, 32), 3, 1), ((2, 2, 18, 24), 2, 2),
+                                       ((1, 2, 24, 15), 5, 3)])
+def test_registered_torch_op_with_an_arbitrary_x0(shape, k, s):
+    """The raw operator with an x0 that is NOT the upsampled input (`converse2d.cpp:165,193`; this is what
+    `test/test_error.py:30` builds): checked against the oracle's closed-form solve."""
+    import conversenet_b200.torch_converse2d  # noqa: F401
+    rng = np.random.default_rng(31)
+    B, C, h, w = shape
+    y = rng.standard_normal(shape).astype(np.float32)
+    x0 = rng.standard_normal((B, C, h * s, w * s)).astype(np.float32)
+    wt, b = orc.init_weight(C, k, rng)
+    b = (b + 0.4 * rng.standard_normal(b.shape)).astype(np.float32)
+    ref = orc.converse2d_solve(y, x0, wt, b, s, 1e-5, dtype=np.float64)
+    out = torch.ops.converse2d.forward(torch.from_numpy(y).cuda(), torch.from_numpy(x0).cuda(),
+                                       torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(), s, 1e-5)
+    assert orc.rel_l2(out.cpu().numpy(), ref) <= TOL_FP32

@@ -140,3 +140,28 @@ def test_emu_gelu_epilogue(emu):
         ref = 0.5 * ref * (1.0 + np.vectorize(erf)(ref / np.sqrt(2.0)))
         out = emu_forward(emu, x, w, b, s, 1, "circular", 1e-5, gelu=1)
         assert orc.rel_l2(out, ref) <= 2e-5
+
+
+@pytest.mark.parametrize("shape,k,s", [((2, 2, 20, 26), 5, 2), ((1, 3, 24, 24), 3, 1), ((1, 2, 18, 22), 2, 2),
+                                       ((1, 2, 15, 20), 5, 3)])
+def test_emu_x0_term_table(emu, shape, k, s):
+    """Table of the arbitrary-x0 term: running the scale-1 forward with it must give
+    IFFT2(FFT2(e) / (alias mean |FK|^2 + lambda)) (`models/util_converse.py:183-184`)."""
+    rng = np.random.default_rng(41)
+    B, C, h, wd = shape
+    e = rng.standard_normal(shape).astype(np.float32)
+    w, b = orc.init_weight(C, k, rng)
+    b = (b + 0.5 * rng.standard_normal(b.shape)).astype(np.float32)
+    table = np.zeros((C * h * wd + h + wd + 6 * 128, 2), np.float32)
+    wf = np.ascontiguousarray(w.reshape(C, k, k), np.float32)
+    bf = np.ascontiguousarray(b.reshape(C), np.float32)
+    emu.emu_build_x0_table.restype = ctypes.c_int
+    assert emu.emu_build_x0_table(_ptr(wf), _ptr(bf), C, k, s, h, wd, ctypes.c_float(1e-5), _ptr(table)) == 0
+    out = np.full(shape, np.nan, np.float32)
+    rc = emu.emu_converse2d_fwd(_ptr(e), _ptr(out), _ptr(table), _ptr(wf), B, C, h, wd, k, 1, 0, PAD["circular"],
+                                0, 96, 0)
+    assert rc == 0
+    FB = orc.psf2otf(w.astype(np.float64), (h * s, wd * s))
+    lam = orc.lam_from_bias(b.astype(np.float64), 1e-5, np.float64)
+    ref = np.real(np.fft.ifft2(np.fft.fft2(e.astype(np.float64)) / (orc.block_mean(np.abs(FB) ** 2, s) + lam)))
+    assert orc.rel_l2(out, ref) <= 2e-6
