@@ -431,6 +431,19 @@ CVB_HD void store_run_f32(void* base, size_t off, const float (&v)[N], bool vec,
 template <int N>
 CVB_HD void store_run_bf16(void* base, size_t off, const float (&v)[N], bool vec, int nvalid) {
   __nv_bfloat16* o = (__nv_bfloat16*)base + off;
+  if constexpr (N % 4 == 0 && N % 8 != 0) {
+    if (vec) {   // 8-byte pieces: a warp still writes one contiguous run of an output row
+#pragma unroll
+      for (int i = 0; i < N; i += 4) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+        uint2 u;
+        u.x = *(unsigned*)&h0; u.y = *(unsigned*)&h1;
+        *(uint2*)(o + i) = u;
+      }
+      return;
+    }
+  }
   if constexpr (N % 8 == 0) {
     if (vec) {
 #pragma unroll
@@ -475,7 +488,7 @@ CVB_HD void epilogue_rows(int tid, int nthr, const float2* sm, const float* wk, 
   constexpr int WIN = DMAX - DMIN + 1;
   constexpr int WC = CW + WIN - 1;
   constexpr int NO = CW * S;
-  constexpr int VEC = sizeof(IO) == 4 ? 4 : 8;  // elements per 16-byte store
+  constexpr int VEC = (sizeof(IO) == 4 || NO % 8 != 0) ? 4 : 8;  // elements per vector store (16 bytes; 8 for short bf16 runs)
   const int p = P.p, h = P.h, w = P.w, pitch = P.pitch;
   const int spr = (P.W + CW - 1) / CW;  // strips per row
   int nseg = nthr / spr;                // row segments handled concurrently
@@ -593,14 +606,15 @@ CVB_HD void run_epilogue(int tid, int nthr, const float2* sm, const float* wk, c
                          const IoArgs& io) {
   const int key = P.s * 100 + P.k;
   switch (key) {
-    // CW cells per thread: CW * S outputs = 16 bytes, so that a warp's store covers
-    // consecutive 16-byte pieces of one output row
-    case 202: epilogue_static<2, 2, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
-    case 203: epilogue_static<2, 3, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
-    case 205: epilogue_static<2, 5, (sizeof(IO) == 4 ? 2 : 4), IO>(tid, nthr, sm, wk, P, io); break;
+    // CW cells per thread: CW * S outputs = 16 bytes of fp32 (8 of bf16: wider runs cost more
+    // window registers than the kernel has), so that a warp's store covers consecutive pieces of
+    // one output row
+    case 202: epilogue_static<2, 2, 2, IO>(tid, nthr, sm, wk, P, io); break;
+    case 203: epilogue_static<2, 3, 2, IO>(tid, nthr, sm, wk, P, io); break;
+    case 205: epilogue_static<2, 5, 2, IO>(tid, nthr, sm, wk, P, io); break;
     case 303: epilogue_static<3, 3, 4, IO>(tid, nthr, sm, wk, P, io); break;
     case 305: epilogue_static<3, 5, 4, IO>(tid, nthr, sm, wk, P, io); break;
-    case 407: epilogue_static<4, 7, (sizeof(IO) == 4 ? 1 : 2), IO>(tid, nthr, sm, wk, P, io); break;
+    case 407: epilogue_static<4, 7, 1, IO>(tid, nthr, sm, wk, P, io); break;
     default: epilogue_generic<IO>(tid, nthr, sm, wk, P, io); break;
   }
 }
