@@ -89,6 +89,8 @@ struct IoArgs {
 };
 
 // ---------------------------------------------------------------- helpers
+// Plain generic loads: the persistent kernel hands these functions its shared-memory prefetch buffers
+// as well as global planes, so no global-only form (ld.global.nc / __ldg) may be used here.
 template <typename IO> CVB_HD float ld_io(const void* p, size_t i);
 template <> CVB_HD float ld_io<float>(const void* p, size_t i) {
   return ((const float*)p)[i];
