@@ -371,7 +371,7 @@ def run_ours(args):
 # ------------------------------------------------------------------ whole networks (extra lines)
 MODEL_CFG = {
     # name: (global batch, input shape per image, fp32 algorithmic GB per global batch with the
-    # fusion-forced accounting 11*C*H*W*e per ConverseBlock, see DESIGN.md)
+    # fusion-forced accounting 11*C*H*W*e per ConverseBlock)
     "dncnn": dict(batch=8, shape=(1, 256, 256), gbytes=29.8, desc="Converse-DnCNN, B8 x 1 x 256 x 256 (config 3)"),
     "srresnet": dict(batch=16, shape=(3, 128, 128), gbytes=30.2, desc="Converse-SRResNet x4, B16 x 3 x 128 x 128 (config 4)"),
     "usrnet": dict(batch=32, shape=(3, 512, 512), gbytes=853.0, desc="Converse-USRNet sf1, B32 x 3 x 512 x 512 (config 5)"),

@@ -1,8 +1,7 @@
 #!/usr/bin/env python3
 """Generate `converse2d_ref_cases.npz` from the UNMODIFIED reference.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with CONVERSE_REFERENCE_ROOT).  Imports the reference's
+Run where the reference checkout is available (its place: CONVERSE_REFERENCE_ROOT).  Imports the reference's
 `models.util_converse.Converse2D` (`backend='pytorch'`), runs it in fp32 and
 fp64 on seeded inputs and stores inputs, parameters and both outputs.  The
 case grid follows the reference's `test/test_error.py:92-98` (B, C, H, W, k, s

@@ -3,7 +3,7 @@ reference helpers (`utils/utils_image.py`) on seeded random images.
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_image_golden.py
 
-Needs the reference tree (default /root/reference, or $CONVERSE_REFERENCE) with numpy, scipy and
+Needs the reference checkout (its place: $CONVERSE_REFERENCE_ROOT) with numpy, scipy and
 OpenCV; writes tests/golden/image_ref_cases.npz (a few KB)."""
 import os
 import sys
@@ -11,7 +11,7 @@ import types
 
 import numpy as np
 
-REF = os.environ.get("CONVERSE_REFERENCE", "/root/reference")
+REF = os.environ.get("CONVERSE_REFERENCE_ROOT", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate `model_ref_cases.npz`: outputs of the UNMODIFIED reference networks.
 
-Imports the reference's model files (default /root/reference), builds each network
+Imports the reference's model files (checkout named by CONVERSE_REFERENCE_ROOT), builds each network
 under `torch.manual_seed(seed)` (random init as the reference's constructors do it),
 runs it in fp32 and fp64 on small seeded inputs and stores inputs, outputs and a
 parameter checksum.  The tests rebuild the same parameters from the same seed with
