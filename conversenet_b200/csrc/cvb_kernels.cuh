@@ -104,6 +104,13 @@ template <> CVB_HD void st_io<__nv_bfloat16>(void* p, size_t i, float v) {
   ((__nv_bfloat16*)p)[i] = __float2bfloat16(v);
 }
 
+CVB_HD float bf16_bits_to_float(unsigned short b) {
+  const uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
 CVB_HD float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
 
 // Index into the unpadded axis of length n for padded coordinate i (already
@@ -223,17 +230,38 @@ CVB_HD void fft_pass(int tid, int nthr, const PassArgs& a, const IoArgs& io, int
     if (flags & PASS_SRC_GLOBAL) {
       // rows base + q*M of padded column `line`, straight from x
       const int cx = io.cmap[line];
+      if constexpr (sizeof(IO) == 2) {
+        // bf16: all 16-bit loads first, the widening to fp32 afterwards, so that every load of the
+        // item is in flight before the first use
+        unsigned short ra[R], rb[R];
 #pragma unroll
-      for (int q = 0; q < R; ++q) {
-        const int ro = io.rmap[base + q * aM];
-        float va = 0.f, vb = 0.f;
-        if ((cx | ro) >= 0) {
-          const size_t off = (size_t)(ro + cx);
-          va = ld_io<IO>(io.xa, off);
-          if (io.xb) vb = ld_io<IO>(io.xb, off);
+        for (int q = 0; q < R; ++q) {
+          const int ro = io.rmap[base + q * aM];
+          ra[q] = 0; rb[q] = 0;
+          if ((cx | ro) >= 0) {
+            const size_t off = (size_t)(ro + cx);
+            ra[q] = ((const unsigned short*)io.xa)[off];
+            if (io.xb) rb[q] = ((const unsigned short*)io.xb)[off];
+          }
         }
-        re[q] = va;
-        im[q] = vb;
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+          re[q] = bf16_bits_to_float(ra[q]);
+          im[q] = bf16_bits_to_float(rb[q]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+          const int ro = io.rmap[base + q * aM];
+          float va = 0.f, vb = 0.f;
+          if ((cx | ro) >= 0) {
+            const size_t off = (size_t)(ro + cx);
+            va = ld_io<IO>(io.xa, off);
+            if (io.xb) vb = ld_io<IO>(io.xb, off);
+          }
+          re[q] = va;
+          im[q] = vb;
+        }
       }
       if (io.ycopy) {  // after all loads are in flight
 #pragma unroll
