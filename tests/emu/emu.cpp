@@ -179,6 +179,12 @@ int emu_converse2d_strip2(const float* x, float* out, const void* table, const f
   return 0;
 }
 
+// the kernels' GELU on an array
+int emu_gelu(const float* in, float* out, int n) {
+  for (int i = 0; i < n; ++i) out[i] = gelu_erf(in[i]);
+  return 0;
+}
+
 // Fused channel-mixing kernels of ConverseBlock, one emulated block of `nthr` threads at a time.
 int emu_ln_pw_gelu(const float* x, float* out, const float* ln_w, const float* ln_b, float eps, const float* w,
                    const float* b, int B, int HW, int nthr) {

@@ -165,3 +165,17 @@ def test_emu_x0_term_table(emu, shape, k, s):
     lam = orc.lam_from_bias(b.astype(np.float64), 1e-5, np.float64)
     ref = np.real(np.fft.ifft2(np.fft.fft2(e.astype(np.float64)) / (orc.block_mean(np.abs(FB) ** 2, s) + lam)))
     assert orc.rel_l2(out, ref) <= 2e-6
+
+
+def test_emu_gelu_matches_the_erf_definition(emu):
+    """The kernels' branch-free GELU against 0.5 x (1 + erf(x / sqrt 2)) in fp64 (`nn.GELU()` of
+    `models/util_converse.py:280-287`): within the rounding of an fp32 result."""
+    from math import erf, sqrt
+    x = np.concatenate([np.linspace(-10, 10, 200001), np.array([0.0, -0.0, 1e-20, -1e-20, 30.0, -30.0])]).astype(np.float32)
+    out = np.empty_like(x)
+    assert emu.emu_gelu(_ptr(x), _ptr(out), x.size) == 0
+    ref = np.array([0.5 * v * (1.0 + erf(v / sqrt(2.0))) for v in x.astype(np.float64)])
+    assert np.abs(out - ref).max() <= 5e-7
+    small = np.abs(x) < 1.0
+    assert np.abs(out[small] - ref[small]).max() <= 1.2e-7
+    assert np.all(out[x > 6] == x[x > 6]) and np.abs(out[x < -6]).max() < 1e-8
