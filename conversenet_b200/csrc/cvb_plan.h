@@ -1,7 +1,6 @@
 // Host-side FFT plan selection, shared by the library and the host-emulation test build.
 #pragma once
 #include <cstring>
-#include <vector>
 #include "cvb_kernels.cuh"
 
 namespace cvb {
@@ -9,25 +8,32 @@ namespace cvb {
 constexpr size_t kSmemLimit = 227 * 1024;
 
 // ------------------------------------------------------------------ plans
+// A short list of radices in fixed storage: plan selection allocates nothing (the entry point
+// for callers that cannot allocate promises a heap-free host side).
+struct RadixList {
+  int v[32];
+  int n = 0;
+  void push(int r) { if (n < 32) v[n] = r; ++n; }   // n > 32 marks an overflow; callers reject it
+  void pop() { --n; }
+};
+
 // Factor n into supported radices: fewest stages, then smallest largest radix,
 // radices in descending order.  Returns false when n has a prime factor above
 // the largest prime butterfly.
-inline bool search(int n, int max_r, std::vector<int>& cur, std::vector<int>& best) {
+inline bool search(int n, int max_r, RadixList& cur, RadixList& best) {
   if (n == 1) {
-    if (best.empty() || cur.size() < best.size() ||
-        (cur.size() == best.size() && cur.front() < best.front())) {
-      best = cur;
-    }
+    if (best.n == 0 || cur.n < best.n || (cur.n == best.n && cur.v[0] < best.v[0])) best = cur;
     return true;
   }
-  if (!best.empty() && cur.size() + 1 > best.size()) return false;
+  if (best.n != 0 && cur.n + 1 > best.n) return false;
+  if (cur.n >= kMaxStages) return false;
   bool any = false;
   for (int i = kNumRadices - 1; i >= 0; --i) {
     const int r = kRadices[i];
     if (r > max_r || n % r) continue;
-    cur.push_back(r);
+    cur.push(r);
     any |= search(n / r, r, cur, best);
-    cur.pop_back();
+    cur.pop();
   }
   return any;
 }
@@ -41,43 +47,46 @@ inline bool make_plan(int n, Plan1D& pl, bool* has_big = nullptr) {
   if (has_big) *has_big = false;
   if (n < 2) return false;
   pl.n = n;
-  std::vector<int> radices;
+  RadixList big;   // ascending while collected, stored descending
   int rest = n;
   for (int f = 29; f <= kMaxBigPrime && f <= rest; f += 2) {
     bool prime = true;
     for (int d = 3; d * d <= f; d += 2) if (f % d == 0) { prime = false; break; }
     if (!prime) continue;
-    while (rest % f == 0) { radices.insert(radices.begin(), f); rest /= f; }
+    while (rest % f == 0) { big.push(f); rest /= f; }
   }
-  if (!radices.empty() && has_big) *has_big = true;
+  if (big.n > kMaxStages) return false;
+  if (big.n > 0 && has_big) *has_big = true;
+  RadixList best;
   if (rest > 1) {
-    std::vector<int> cur, best;
+    RadixList cur;
     search(rest, 1 << 30, cur, best);
-    if (best.empty()) return false;
-    radices.insert(radices.end(), best.begin(), best.end());
+    if (best.n == 0) return false;
   }
-  if ((int)radices.size() > kMaxStages) return false;
-  pl.nst = (int)radices.size();
+  if (big.n + best.n > kMaxStages) return false;
+  pl.nst = big.n + best.n;
   int L = n;
   for (int i = 0; i < pl.nst; ++i) {
-    pl.radix[i] = radices[i];
+    const int r = i < big.n ? big.v[big.n - 1 - i] : best.v[i - big.n];
+    pl.radix[i] = r;
     pl.L[i] = L;
-    pl.M[i] = L / radices[i];
-    L /= radices[i];
+    pl.M[i] = L / r;
+    L /= r;
   }
   return true;
 }
 
 // ---- Rader tables for a large prime in the first stage of an axis plan ----
 inline int primitive_root(int R) {
-  std::vector<int> fac;
+  int fac[16], nfac = 0;
   int m = R - 1;
   for (int f = 2; f * f <= m; ++f)
-    if (m % f == 0) { fac.push_back(f); while (m % f == 0) m /= f; }
-  if (m > 1) fac.push_back(m);
+    if (m % f == 0) { if (nfac < 16) fac[nfac++] = f; while (m % f == 0) m /= f; }
+  if (m > 1 && nfac < 16) fac[nfac++] = m;
   for (int g = 2; g < R; ++g) {
     bool ok = true;
-    for (int f : fac) {
+    for (int fi = 0; fi < nfac; ++fi) {
+      const int f = fac[fi];
       long long r = 1, b = g; int e = (R - 1) / f;
       while (e) { if (e & 1) r = r * b % R; b = b * b % R; e >>= 1; }
       if (r == 1) { ok = false; break; }

@@ -155,11 +155,18 @@ int cvb_pw_res_fwd(const void* t, const void* res, void* out, const float* w, co
  * ends).  Meant for code that runs where an allocator call is impossible or unwelcome:
  * a plug-in that owns nothing but its input and output buffers, a region whose memory
  * pool must not change, a real-time loop that may not take the allocator lock.  The
- * function calls no cudaMalloc / cudaFree and no allocating library routine.
+ * function calls no cudaMalloc / cudaFree and no allocating library routine, and its
+ * host side works in fixed-size stack storage (no heap allocation either).
  *   - Limit: one padded plane pair, 8*(H+2p)*(W+2p) bytes, must fit the array
  *     (about 1440 x 1440); larger planes return CVB_ERR_TOO_LARGE.
- *   - The first call on each device looks up the array's device address (a runtime
- *     query, no allocation); make that first call outside any stream capture.
+ *   - Set-up on first use: the first call on each device looks up the device addresses
+ *     of the array and of the status word (runtime queries, no allocation), and the
+ *     first call per device that meets a padded length with a large prime factor (268,
+ *     for instance) also runs one small kernel that fills a constant table inside the
+ *     library and waits for it on `stream` (cudaStreamSynchronize).  Make those first
+ *     calls outside any stream capture.
+ *   - A bounded wait that gives up inside a kernel is reported through
+ *     cvb_last_device_status, as for cvb_converse2d_fwd.
  *   - All calls share the one array and it keeps the previous call's contents.  Nothing
  *     in it has to start at zero (every element is written before it is read), but two
  *     calls that overlap on the GPU -- different streams, or different host threads --

@@ -69,6 +69,9 @@ def test_argument_validation_without_device(lib):
     assert f(one, one, one, None, 1, 1, 8, 8, 3, 2, 1, 0, 0, 0, None, 0, None) == -1
     assert lib.cvb_build_transfer(None, one, 1, 3, 1, 8, 8, 1e-5, one, None) == -1
     assert lib.cvb_build_transfer(one, one, 1, 9, 1, 8, 8, 1e-5, one, None) == -6
+    # kernel_size above the 15 taps the table build keeps per thread: refused before any launch
+    assert lib.cvb_build_transfer(one, one, 1, 17, 1, 32, 32, 1e-5, one, None) == -6
+    assert lib.cvb_build_x0_table(one, one, 1, 17, 1, 32, 32, 1e-5, one, None) == -6
     assert lib.cvb_transfer_bytes(2, 68, 68) == (2 * 68 * 68 + 136) * 8
     assert lib.cvb_transfer_bytes(0, 68, 68) == 0
 

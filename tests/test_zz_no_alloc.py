@@ -62,6 +62,7 @@ def test_static_scratch_entry_matches_regular_entry(cfg):
     assert _call_static(lib, cfg, xd, table, wf, out1) == 0
     assert _call_static(lib, cfg, xd2, table, wf, out2) == 0
     torch.cuda.synchronize()
+    assert lib.cvb_last_device_status(1) == 0   # no bounded wait gave up inside the kernels
     assert orc.rel_l2(out1.cpu().numpy(), ref.cpu().numpy()) <= TOL
     assert orc.rel_l2(out2.cpu().numpy(), ref2.cpu().numpy()) <= TOL
     oracle = orc.converse2d_forward(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"], dtype=np.float64)
