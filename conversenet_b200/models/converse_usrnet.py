@@ -47,10 +47,18 @@ class ConvReverseDataNet(nn.Module):
         self.biaseps = torch.sigmoid(self.alpha.detach() - 9.0) + self.eps
         ks = k.size(2)
         h, w = H + 2 * padding, W + 2 * padding
-        weight = k.detach().reshape(1, B * C, ks, ks)
-        bias = self.alpha.detach().expand(B, C, 1, 1).reshape(1, B * C, 1, 1)
+        weight = k.reshape(1, B * C, ks, ks)
+        bias = self.alpha.expand(B, C, 1, 1).reshape(1, B * C, 1, 1)
         table, wf = CF.build_transfer(weight, bias, int(sf), self.eps, h, w)
-        out = CF.converse2d_forward(x.reshape(1, B * C, H, W), table, wf, ks, int(sf), padding, padding_mode)
+        planes = x.reshape(1, B * C, H, W)
+        if torch.is_grad_enabled() and (x.requires_grad or k.requires_grad or self.alpha.requires_grad):
+            # differentiable in x, the kernels and alpha, as the reference's torch.fft data step is
+            # (`models/converse_usrnet.py:41-68`)
+            from ..autograd import Converse2DFunction
+            out = Converse2DFunction.apply(planes, weight, bias, table, wf, ks, int(sf), padding, padding_mode,
+                                           self.eps)
+        else:
+            out = CF.converse2d_forward(planes, table, wf, ks, int(sf), padding, padding_mode)
         return out.reshape(B, C, H * int(sf), W * int(sf))
 
 

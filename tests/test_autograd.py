@@ -1,12 +1,98 @@
-"""Gradients of Converse2D: the torch.fft restatement against the numpy oracle (CPU), and the native
-dL/dx against autograd through that restatement (GPU; the comparison `test/test_error.py:50-54` of the
-reference makes between its two backends)."""
+"""Gradients of Converse2D against gradients of the unmodified reference.
+
+`tests/golden/converse2d_ref_grads.npz` (written by tests/golden/make_golden.py from the imported
+reference, fp64, loss = y^2 mean: the protocol of the reference's `test/test_error.py:50-54`, plus its
+gradcheck case `:140-153`) holds dL/dx, dL/dweight and dL/dbias.  CPU: the torch.fft restatement that
+supplies parameter gradients is pinned to them; GPU: the module's gradients (native dL/dx) are."""
+import ast
+import os
+
 import numpy as np
 import pytest
 import torch
 
 from conversenet_b200.autograd import spectral_forward
 from oracle import converse2d_oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _grad_cases():
+    z = np.load(os.path.join(ROOT, "tests", "golden", "converse2d_ref_grads.npz"))
+    return z, ast.literal_eval(str(z["meta"]))
+
+
+N_GRAD_CASES = 8
+
+
+@pytest.mark.parametrize("j", range(N_GRAD_CASES))
+def test_restatement_gradients_match_reference_gradients(j):
+    z, meta = _grad_cases()
+    assert len(meta) == N_GRAD_CASES
+    c = meta[j]
+    x = torch.from_numpy(z[f"x{j}"]).double().requires_grad_(True)
+    w = torch.from_numpy(z[f"w{j}"]).double().requires_grad_(True)
+    b = torch.from_numpy(z[f"b{j}"]).double().requires_grad_(True)
+    y = spectral_forward(x, w, b, c["s"], c["p"], c["mode"], c["eps"])
+    gx, gw, gb = torch.autograd.grad(y.square().mean(), (x, w, b))
+    assert orc.rel_l2(y.detach().numpy(), z[f"y{j}"]) <= 1e-9
+    assert orc.rel_l2(gx.numpy(), z[f"gx{j}"]) <= 1e-8
+    assert orc.rel_l2(gw.numpy(), z[f"gw{j}"]) <= 1e-7
+    # dL/dbias is ~1e-12 where lambda is dominated by eps; the reference's own fp64 value then carries
+    # the cancellation noise of its division by lambda (`models/util_converse.py:186`), ~1e-15 absolute
+    rb = z[f"gb{j}"]
+    assert float(np.linalg.norm(gb.numpy() - rb)) <= 1e-7 * float(np.linalg.norm(rb)) + 1e-14
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("j", range(N_GRAD_CASES))
+def test_module_gradients_match_reference_gradients(j):
+    from conversenet_b200 import Converse2D
+    z, meta = _grad_cases()
+    c = meta[j]
+    m = Converse2D(c["C"], c["C"], c["k"], scale=c["s"], padding=c["p"], padding_mode=c["mode"], eps=c["eps"]).cuda()
+    with torch.no_grad():
+        m.weight.copy_(torch.from_numpy(z[f"w{j}"]))
+        m.bias.copy_(torch.from_numpy(z[f"b{j}"]))
+    x = torch.from_numpy(z[f"x{j}"]).cuda().requires_grad_(True)
+    y = m(x)
+    gx, gw, gb = torch.autograd.grad(y.square().mean(), (x, m.weight, m.bias))
+    assert orc.rel_l2(y.detach().cpu().numpy(), z[f"y{j}"]) <= 1e-4
+    assert orc.rel_l2(gx.cpu().numpy(), z[f"gx{j}"]) <= 1e-4     # native adjoint
+    assert orc.rel_l2(gw.cpu().numpy(), z[f"gw{j}"]) <= 1e-3     # parameter gradients in fp32
+    rb = z[f"gb{j}"]
+    # dL/dbias carries sigmoid'(bias - 9), ~1e-4 at the default bias: below fp32 resolution of the loss
+    assert float(np.linalg.norm(gb.cpu().numpy().astype(np.float64) - rb)) <= 1e-3 * float(np.linalg.norm(rb)) + 1e-8
+
+
+@pytest.mark.gpu
+def test_usrnet_data_step_is_differentiable():
+    """The data step with per-sample kernels: gradients reach x, the kernels and alpha, as in the
+    reference (`models/converse_usrnet.py:41-68`, torch.fft under autograd)."""
+    from conversenet_b200.models.converse_usrnet import ConvReverseDataNet
+    torch.manual_seed(4)
+    B, C, H, W, ks = 2, 64, 16, 20, 7
+    d = ConvReverseDataNet().cuda()
+    with torch.no_grad():
+        d.alpha.copy_(9.0 + torch.randn_like(d.alpha))
+    k = torch.softmax(torch.randn(B, C, ks * ks, device="cuda"), -1).view(B, C, ks, ks).requires_grad_(True)
+    x = torch.randn(B, C, H, W, device="cuda", requires_grad=True)
+    for sf in (1, 2):
+        out = d(x, k, sf)
+        assert out.grad_fn is not None
+        gx, gk, ga = torch.autograd.grad(out.square().mean(), (x, k, d.alpha))
+        x64 = x.detach().double().requires_grad_(True)
+        k64 = k.detach().double().requires_grad_(True)
+        a64 = d.alpha.detach().double().requires_grad_(True)
+        ref = spectral_forward(x64.reshape(1, B * C, H, W), k64.reshape(1, B * C, ks, ks),
+                               a64.expand(B, C, 1, 1).reshape(1, B * C, 1, 1), sf, 0, "circular", d.eps)
+        rx, rk, ra = torch.autograd.grad(ref.square().mean(), (x64, k64, a64))
+        rel = lambda a, r: float((a.detach().double() - r).norm() / r.norm())
+        assert rel(out.reshape(1, B * C, H * sf, W * sf), ref) <= 1e-4
+        assert rel(gx, rx) <= 1e-4
+        assert rel(gk, rk) <= 1e-3
+        assert rel(ga, ra) <= 1e-2
+
 
 CASES = [
     # B, C, H, W, k, s, p, mode

@@ -20,7 +20,7 @@ def _run(args, timeout=600):
 def test_reference_arm_line():
     if not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "converse2d_ref.so")):
         pytest.skip("oracle/_ref not built")
-    r = _run(["--impl", "reference", "--steps", "1", "--warmup", "1"])
+    r = _run(["--impl", "reference", "--steps", "1", "--warmup", "1", "--models", "none"])
     assert r.returncode == 0, r.stderr[-800:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["metric"] == "converse2d_fwd_throughput"
@@ -37,3 +37,14 @@ def test_ours_arm_needs_a_gpu():
     r = _run(["--steps", "1", "--warmup", "1"], timeout=300)
     assert r.returncode != 0
     assert "CUDA" in (r.stderr + r.stdout)
+
+
+def test_both_arms_share_metric_and_config():
+    import argparse
+    import bench
+    a = argparse.Namespace(gpus=1, steps=3, warmup=1)
+    ours, ref = bench.base_line(a), bench.base_line(a, "reference")
+    assert ref["impl"] == "reference" and "impl" not in ours
+    for key in ("metric", "unit", "higher_is_better", "config", "scaling", "dtype", "data"):
+        assert ours[key] == ref[key]
+    assert set(bench.BENCH_MODELS) <= set(bench.MODEL_CFG)

@@ -1,0 +1,101 @@
+"""Whole networks at the resolutions of the benchmark configurations against the unmodified
+reference (`tests/golden/model_fullsize_cases.npz`, written by
+tests/golden/make_model_fullsize_golden.py from the imported reference, batch 1).
+
+At these sizes the planes take the kernels the benchmark configurations use: 268 x 268 (the
+67-point stage on the tensor cores), 136 / 264 / 260 / 520 (SRResNet), 516 with a Rader stage and
+512 with per-sample tables (USRNet, scale 1 and scale 4).  Both parameter sets of the fixture are
+checked: seeded random init (re-created here from the same seed, guarded by a checksum) and the
+reference's trained checkpoints (copies under tests/golden/model_zoo, loaded strictly).
+
+Bar (fp32): rel. L2 against the reference's fp64 output <= max(1e-4, drift), drift = the
+reference's own fp32-vs-fp64 distance stored with the case (its division by lambda makes the fp32
+reference noisy: 2e-5 .. 3e-3 at depth).  bf16: against the fp32 reference fed the bf16-rounded
+input with its output rounded to bf16 (torch.fft has no bf16)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import bench
+from oracle import converse2d_oracle as orc
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ZOO = os.path.join(ROOT, "tests", "golden", "model_zoo")
+CASES = [  # case, workload of bench.synthetic_batch, checkpoint, construction seed  (as in the generator)
+    ("dncnn", "dncnn", "converse_dncnn.pth", 201),
+    ("srresnet", "srresnet", "converse_srresnet.pth", 202),
+    ("usrnet_sf1", "usrnet_sf1", "converse_usrnet.pth", 203),
+    ("usrnet_sf4", "usrnet_sf4", "converse_usrnet.pth", 203),
+    ("conversenet", "conversenet", "conversenet.pth", 204),
+]
+
+
+@pytest.fixture(scope="module")
+def fx():
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return np.load(os.path.join(ROOT, "tests", "golden", "model_fullsize_cases.npz"))
+
+
+def _network(name, pset, ckpt, seed):
+    from conversenet_b200 import models
+    ctor = {"dncnn": models.ConverseDnCNN, "srresnet": models.ConverseMSRResNet, "usrnet": models.ConverseUSRNet,
+            "conversenet": models.ConverseNet}[bench.network_name(name)]
+    torch.manual_seed(seed)
+    m = ctor().eval()
+    if pset == "rand":
+        bench.seed_alphas(m, 5)
+    else:
+        m.load_state_dict(torch.load(os.path.join(ZOO, ckpt), map_location="cpu"), strict=True)
+    return m
+
+
+def _run(m, x, extra, dtype=torch.float32):
+    m = m.cuda().to(dtype)
+    args = [torch.from_numpy(x).cuda().to(dtype)]
+    if extra:
+        args += [torch.from_numpy(extra[0]).cuda().to(dtype), extra[1]]
+    with torch.no_grad():
+        out = m(*args)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("pset", ["ckpt", "rand"])
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_network_at_benchmark_resolution(fx, case, pset):
+    name, wl, ckpt, seed = case
+    key = "%s_%s" % (name, pset)
+    x, extra = bench.synthetic_batch(wl, 1, 700 + seed)
+    assert abs(float(x.astype(np.float64).sum()) - float(fx[key + "_insum"])) <= 1e-6 * abs(float(fx[key + "_insum"]))
+    m = _network(name, pset, ckpt, seed)
+    psum = float(sum(p.detach().double().abs().sum() for p in m.parameters()))
+    assert abs(psum - float(fx[key + "_psum"])) <= 1e-6 * float(fx[key + "_psum"])
+    out = _run(m, x, extra)
+    st = int(fx["stride"])
+    sub, drift = fx[key + "_sub"], float(fx[key + "_drift"])
+    assert out[..., ::st, ::st].shape == sub.shape
+    err = orc.rel_l2(out[..., ::st, ::st], sub)
+    print("%s: rel L2 vs reference fp64 %.2e (reference fp32 drift %.2e)" % (key, err, drift))
+    assert err <= max(1e-4, drift)
+    norm = float(fx[key + "_norm"])
+    assert abs(float(np.linalg.norm(out.astype(np.float64))) - norm) <= max(1e-4, drift) * norm
+    from conversenet_b200 import _cabi
+    assert _cabi.load().cvb_last_device_status(1) == 0
+
+
+def test_dncnn_bf16_at_benchmark_resolution(fx):
+    """bf16 tensors end to end (parameters, activations between kernels; spectra and accumulation fp32).
+    Twenty blocks each round their 64-channel stream and 128-channel branch tensors to bf16 (2^-9 per
+    rounding), so the network-level distance is several times the single-layer bar of 5e-3."""
+    name, wl, ckpt, seed = CASES[0]
+    x, extra = bench.synthetic_batch(wl, 1, 700 + seed)
+    m = _network(name, "ckpt", ckpt, seed)
+    out = _run(m, x, extra, torch.bfloat16)
+    st = int(fx["stride"])
+    err = orc.rel_l2(out[..., ::st, ::st], fx["dncnn_ckpt_bf16_sub"])
+    print("dncnn bf16: rel L2 vs reference (bf16-rounded input and output) %.2e" % err)
+    assert err <= 3e-2
