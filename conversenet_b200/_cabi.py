@@ -12,6 +12,7 @@ LIB_PATH = os.environ.get("CVB_LIBRARY") or os.path.join(_HERE, "libconverse_b20
 
 PAD_MODES = {"circular": 0, "replicate": 1, "reflect": 2, "constant": 3}
 CVB_F32, CVB_BF16 = 0, 1
+OPT_RUNTIME_PLAN, OPT_MULTIPASS, OPT_PERSISTENT, OPT_BLOCK_KERNELS = 0, 1, 2, 3
 
 # name -> (restype, argtypes); one line per declaration in include/converse_b200.h
 _c = ctypes
@@ -19,6 +20,8 @@ SIGNATURES = {
     "cvb_version": (_c.c_int, []),
     "cvb_strerror": (_c.c_char_p, [_c.c_int]),
     "cvb_last_cuda_error": (_c.c_int, []),
+    "cvb_set_option": (_c.c_int, [_c.c_int, _c.c_int]),
+    "cvb_get_option": (_c.c_int, [_c.c_int]),
     "cvb_last_device_status": (_c.c_int, [_c.c_int]),
     "cvb_transfer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int, _c.c_int]),
     "cvb_build_transfer": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
@@ -70,3 +73,20 @@ def check(status, what):
         if status == -5:
             extra = " (cudaError %d)" % lib.cvb_last_cuda_error()
         raise RuntimeError("%s failed: %s%s" % (what, msg, extra))
+
+
+class option:
+    """`with option(OPT_MULTIPASS, 1): ...` -- set a routing option of the library for a block of code."""
+
+    def __init__(self, which, value):
+        self.which, self.value = which, value
+
+    def __enter__(self):
+        lib = load()
+        self.old = lib.cvb_get_option(self.which)
+        check(lib.cvb_set_option(self.which, self.value), "cvb_set_option")
+        return self
+
+    def __exit__(self, *exc):
+        load().cvb_set_option(self.which, self.old)
+        return False

@@ -13,7 +13,16 @@ int cuda_fail(cudaError_t e);
     if (e__ != cudaSuccess) return ::cvb::cuda_fail(e__); \
   } while (0)
 
+// Tuning aids read the environment only in tuning builds (-DCVB_TUNING); a shipped library ignores them.
+#ifdef CVB_TUNING
 int env_int(const char* name, int dflt);
+#define CVB_TUNE(name, dflt) ::cvb::env_int(name, dflt)
+#else
+#define CVB_TUNE(name, dflt) (dflt)
+#endif
+
+// Process-wide routing options (cvb_set_option / cvb_get_option in the C ABI).
+int option(int which);
 int sm_count();  // multiprocessors of the current device
 
 // Number of (channel, batch-pair) work items = blocks of the shared-memory kernels.
@@ -47,6 +56,14 @@ struct Strip2Entry {
   int r0, r1, s0, s1;  // axis length r0 * r1; Rader sub-plan s0 * s1 of r0 - 1 (0, 0 if r0 is a register radix)
   Strip2Launcher A, B, C;
   Strip2Resident Q;
+};
+
+// Tensor-core multi-pass kernels (k_gemmdft.cu, one object per registry line).
+namespace gd { struct Params; }
+typedef int (*GdLauncher)(const gd::Params& P, int io_dtype, cudaStream_t st);
+struct GdEntry {
+  int r0;
+  GdLauncher A, B1, B2, C;
 };
 
 // Compile-time-plan kernels (k_static.cu, one object per registry line).

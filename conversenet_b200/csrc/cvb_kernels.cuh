@@ -45,6 +45,7 @@ struct Plan1D {
   int radix[kMaxStages];
   int L[kMaxStages];  // sub-transform length entering stage i
   int M[kMaxStages];  // L / radix
+  int gemm;           // 1: plan {n / 4, 4} of the tensor-core multi-pass kernels (cvb_gemmdft.cuh)
 };
 
 struct FwdParams {

@@ -1,5 +1,6 @@
 // Host-side FFT plan selection, shared by the library and the host-emulation test build.
 #pragma once
+#include <cstdlib>
 #include <cstring>
 #include "cvb_kernels.cuh"
 
@@ -76,6 +77,48 @@ inline bool make_plan(int n, Plan1D& pl, bool* has_big = nullptr) {
   return true;
 }
 
+// ---- plans of the tensor-core multi-pass kernels: n = 4 * R0 with R0 in the registry ----
+inline bool gemm_axis(int n) {
+  if (n % 4) return false;
+  static const int r0s[] = {
+#define CVB_GEMM(r0) r0,
+#include "gemm_registry.inc"
+#undef CVB_GEMM
+  };
+  for (int r : r0s) if (n / 4 == r) return true;
+  return false;
+}
+inline void make_gemm_plan(int n, Plan1D& pl) {
+  memset(&pl, 0, sizeof(pl));
+  pl.n = n; pl.nst = 2; pl.gemm = 1;
+  pl.radix[0] = n / 4; pl.L[0] = n; pl.M[0] = 4;
+  pl.radix[1] = 4; pl.L[1] = 4; pl.M[1] = 1;
+}
+inline bool gemm_disabled() {   // tuning builds: CVB_NO_GEMM=1 takes the register-FFT multi-pass kernels instead
+#ifdef CVB_TUNING
+  const char* v = getenv("CVB_NO_GEMM");
+  return v && *v && *v != '0';
+#else
+  return false;
+#endif
+}
+// Plans of both axes of a padded plane.  A plane whose two lengths are in the registry takes the
+// tensor-core multi-pass kernels whatever its scale or tap count (the transfer table is laid out
+// for the plan, so the choice may depend on nothing but h and w).
+inline bool make_axis_plans(int h, int w, Plan1D& py, Plan1D& px, bool* big = nullptr) {
+  if (big) *big = false;
+  if (gemm_axis(h) && gemm_axis(w) && !gemm_disabled()) {
+    make_gemm_plan(h, py);
+    make_gemm_plan(w, px);
+    if (big) *big = true;
+    return true;
+  }
+  bool by = false, bx = false;
+  if (!make_plan(h, py, &by) || !make_plan(w, px, &bx)) return false;
+  if (big) *big = by || bx;
+  return true;
+}
+
 // ---- Rader tables for a large prime in the first stage of an axis plan ----
 inline int primitive_root(int R) {
   int fac[16], nfac = 0;
@@ -101,7 +144,7 @@ inline RaderInfo rader_for(const Plan1D& pl, int off) {
   RaderInfo r;
   memset(&r, 0, sizeof(r));
   r.off = off;
-  if (pl.nst < 1 || pl.radix[0] <= 26) return r;
+  if (pl.nst < 1 || pl.radix[0] <= 26 || pl.gemm) return r;
   bool big = false;
   if (!make_plan(pl.radix[0] - 1, r.sub, &big) || big) return r;
   r.g = primitive_root(pl.radix[0]);

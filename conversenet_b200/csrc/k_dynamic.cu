@@ -15,7 +15,7 @@ namespace {
 template <typename IO>
 int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
   CVB_CUDA(cudaFuncSetAttribute(smem_dynamic_kernel<IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int nthr = env_int("CVB_THREADS", 0);
+  int nthr = CVB_TUNE("CVB_THREADS", 0);
   if (nthr <= 0) {
     // enough threads for the stage with the fewest butterflies, at most 512
     const int by = P.w * (P.h / P.py.radix[0]), bx = P.h * (P.w / P.px.radix[0]);

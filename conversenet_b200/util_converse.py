@@ -11,6 +11,11 @@ import torch.nn.functional as F
 from . import functional as CF
 
 
+# False: ConverseBlock runs its layers one by one (PyTorch LayerNorm / 1x1 / GELU around the native
+# operator) instead of the fused block kernels; the tests compare the two.
+BLOCK_FUSION = True
+
+
 class LayerNorm(nn.Module):
     """channels_last / channels_first LayerNorm (`models/util_converse.py:42-68`)."""
 
@@ -165,7 +170,7 @@ class ConverseBlock(nn.Module):
         return (x.is_cuda and x.dim() == 4 and x.size(1) == 64 and c1[1].out_channels == 128 and
                 c1[5].out_channels == 64 and c1[3].scale == 1 and x.dtype in (torch.float32, torch.bfloat16) and
                 c1[1].bias is not None and c1[5].bias is not None and c2[1].bias is not None and
-                c2[3].bias is not None and os.environ.get("CVB_NO_BLOCK_FUSION", "") != "1")
+                c2[3].bias is not None and BLOCK_FUSION)
 
     def _forward_fused(self, x, alpha1=None, alpha2=None):
         # three kernels per block: LN+1x1+GELU, Converse2D(+GELU), 1x1+residual+LN+1x1+GELU+1x1+residual

@@ -52,6 +52,23 @@ const char* cvb_strerror(int status);
 int cvb_last_cuda_error(void);
 
 /*
+ * Process-wide routing options.  The defaults are what a caller wants; the options exist so that
+ * every kernel family can be reached on any size (the tests compare the routes with one another).
+ * They take the place of the reference's CONVERSE2D_BACKEND switch (models/util_converse.py:150),
+ * which chooses between its two implementations per call.  Not thread-safe against calls in flight.
+ */
+enum {
+  CVB_OPT_RUNTIME_PLAN = 0,   /* 1: planes that fit shared memory take the run-time-plan kernel     */
+  CVB_OPT_MULTIPASS = 1,      /* 1: every plane takes the multi-pass path through the workspace     */
+  CVB_OPT_PERSISTENT = 2,     /* 1: compile-time-plan kernels run as persistent blocks with prefetch */
+  CVB_OPT_BLOCK_KERNELS = 3,  /* ConverseBlock 1x1 kernels: 0 CUDA cores, 1 tcgen05 single-buffered,
+                                 2 tcgen05 warp-specialised (default)                               */
+  CVB_OPT_COUNT_ = 4
+};
+int cvb_set_option(int which, int value);   /* CVB_OK or CVB_ERR_BAD_ARGUMENT */
+int cvb_get_option(int which);              /* the value, or CVB_ERR_BAD_ARGUMENT */
+
+/*
  * Device-side status of the current device: 0, or non-zero after a kernel gave up a
  * bounded wait (its output is then incomplete).  Synchronises the device; clears the
  * word when `clear` is non-zero.  Negative on a runtime error.  (The reference has no

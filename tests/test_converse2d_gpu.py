@@ -38,10 +38,11 @@ def test_golden_cases(golden, i):
 
 
 @pytest.mark.parametrize("i", [1, 4, 13, 15])
-def test_golden_cases_forced_runtime_plan(golden, i, monkeypatch):
-    monkeypatch.setenv("CVB_FORCE_DYNAMIC", "1")
+def test_golden_cases_forced_runtime_plan(golden, i):
+    from conversenet_b200 import _cabi
     c, x, w, b, ref32, ref64 = golden.case(i)
-    out = _run(x, w, b, c["s"], c["p"], c["mode"], c["eps"])
+    with _cabi.option(_cabi.OPT_RUNTIME_PLAN, 1):
+        out = _run(x, w, b, c["s"], c["p"], c["mode"], c["eps"])
     assert orc.rel_l2(out, ref64) <= TOL_FP32
 
 
@@ -98,19 +99,18 @@ def test_tensor_core_stage_bf16_io_and_status_word():
     assert lib.cvb_last_device_status(0) == 0
 
 
-def test_forced_multi_pass_matches_shared_memory_path(monkeypatch):
+def test_forced_multi_pass_matches_shared_memory_path():
+    from conversenet_b200 import _cabi
     cfg = CONFIGS["odd_batch"]
     x, w, b = _seeded(cfg, 6)
     for s in (1, 2):
         a = _run(x, w, b, s, cfg["p"], cfg["mode"], cfg["eps"])
-        monkeypatch.setenv("CVB_FORCE_STRIP", "1")
-        d = _run(x, w, b, s, cfg["p"], cfg["mode"], cfg["eps"])
-        monkeypatch.delenv("CVB_FORCE_STRIP")
+        with _cabi.option(_cabi.OPT_MULTIPASS, 1):
+            d = _run(x, w, b, s, cfg["p"], cfg["mode"], cfg["eps"])
         assert orc.rel_l2(d, a) <= 2e-6
     xb = torch.from_numpy(x).bfloat16().float().numpy()
-    monkeypatch.setenv("CVB_FORCE_STRIP", "1")
-    d = _run(xb, w, b, 2, cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
-    monkeypatch.delenv("CVB_FORCE_STRIP")
+    with _cabi.option(_cabi.OPT_MULTIPASS, 1):
+        d = _run(xb, w, b, 2, cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
     a = _run(xb, w, b, 2, cfg["p"], cfg["mode"], cfg["eps"], dtype=torch.bfloat16)
     assert orc.rel_l2(d, a) <= 5e-3
 
@@ -145,27 +145,27 @@ def test_baseline_configs_bf16_io(name):
     assert orc.rel_l2(out, ref) <= TOL_BF16
 
 
-def test_forced_runtime_plan_matches_compiled_plan(monkeypatch):
+def test_forced_runtime_plan_matches_compiled_plan():
+    from conversenet_b200 import _cabi
     cfg = CONFIGS["odd_batch"]
     x, w, b = _seeded(cfg, 5)
     a = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
-    monkeypatch.setenv("CVB_FORCE_DYNAMIC", "1")
-    d = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+    with _cabi.option(_cabi.OPT_RUNTIME_PLAN, 1):
+        d = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
     assert orc.rel_l2(a, d) <= 2e-6
 
 
-def test_persistent_prefetch_kernel_matches(monkeypatch):
+def test_persistent_prefetch_kernel_matches():
     # blocks looping over plane pairs with bulk-copy (TMA) prefetch of x; bounded waits must not trip
     from conversenet_b200 import _cabi
     cfg = dict(CONFIGS["cfg2"], B=12)
     x, w, b = _seeded(cfg, 21)
     base = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
-    monkeypatch.setenv("CVB_PERSIST", "1")
-    pers = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
-    assert _cabi.load().cvb_last_device_status(1) == 0
-    assert orc.rel_l2(pers, base) <= 1e-6
-    pers1 = _run(x, w, b, 1, cfg["p"], cfg["mode"], cfg["eps"])
-    monkeypatch.setenv("CVB_PERSIST", "0")
+    with _cabi.option(_cabi.OPT_PERSISTENT, 1):
+        pers = _run(x, w, b, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+        assert _cabi.load().cvb_last_device_status(1) == 0
+        assert orc.rel_l2(pers, base) <= 1e-6
+        pers1 = _run(x, w, b, 1, cfg["p"], cfg["mode"], cfg["eps"])
     base1 = _run(x, w, b, 1, cfg["p"], cfg["mode"], cfg["eps"])
     assert _cabi.load().cvb_last_device_status(1) == 0
     assert orc.rel_l2(pers1, base1) <= 1e-6

@@ -89,6 +89,7 @@ def test_conversenet_blind(fx):
 def test_fused_block_matches_unfused(monkeypatch):
     # ConverseBlock through the three fused kernels vs the same module with torch's LayerNorm / 1x1 / GELU
     from conversenet_b200 import ConverseBlock, ConverseBlockAlphaVariant
+    from conversenet_b200 import util_converse as uc
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     for cls in (ConverseBlock, ConverseBlockAlphaVariant):
@@ -103,9 +104,9 @@ def test_fused_block_matches_unfused(monkeypatch):
         x = torch.randn(3, 64, 37, 29, device="cuda")
         with torch.no_grad():
             fused = blk(x)
-            monkeypatch.setenv("CVB_NO_BLOCK_FUSION", "1")
+            monkeypatch.setattr(uc, "BLOCK_FUSION", False)
             plain = blk(x)
-            monkeypatch.delenv("CVB_NO_BLOCK_FUSION")
+            monkeypatch.setattr(uc, "BLOCK_FUSION", True)
         assert float((fused - plain).norm() / plain.norm()) <= 5e-6
         with torch.no_grad():
             fb = blk(x.bfloat16()).float()
@@ -123,11 +124,11 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
         ln.weight.add_(0.3 * torch.randn_like(ln.weight))
         ln.bias.add_(0.2 * torch.randn_like(ln.bias))
     x = torch.randn(3, 64, 64, 96, device="cuda")   # 6144 pixels per image: whole 128-pixel tiles
-    monkeypatch.setenv("CVB_TC", "0")
-    ref = CF.ln_pw_gelu(x, ln, conv)
-    monkeypatch.setenv("CVB_TC", "1")    # single-buffered kernel
-    out1 = CF.ln_pw_gelu(x, ln, conv)
-    monkeypatch.setenv("CVB_TC", "2")    # warp-specialised, double-buffered kernel (the default)
+    with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 0):
+        ref = CF.ln_pw_gelu(x, ln, conv)
+    with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 1):    # single-buffered kernel
+        out1 = CF.ln_pw_gelu(x, ln, conv)
+    assert _cabi.load().cvb_get_option(_cabi.OPT_BLOCK_KERNELS) == 2   # warp-specialised, double-buffered: default
     out = CF.ln_pw_gelu(x, ln, conv)
     torch.cuda.synchronize()
     assert _cabi.load().cvb_last_device_status(1) == 0
@@ -139,9 +140,9 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
     t = torch.randn(3, 128, 64, 96, device="cuda")
     torch.backends.cudnn.allow_tf32 = False
     want2 = x + alpha * conv2(t)
-    for mode in ("1", "2"):
-        monkeypatch.setenv("CVB_TC", mode)
-        got2 = CF.pw_res(t, x, conv2, alpha)
+    for mode in (1, 2):
+        with _cabi.option(_cabi.OPT_BLOCK_KERNELS, mode):
+            got2 = CF.pw_res(t, x, conv2, alpha)
         assert float((got2 - want2).norm() / want2.norm()) <= 5e-6
     assert _cabi.load().cvb_last_device_status(1) == 0
     # torch fp32 reference of the same op
