@@ -588,7 +588,12 @@ def product_network(workload, dev, tdtype):
     net = ctor()
     seed_alphas(net)
     net = net.to(dev).eval()
-    return net.to(tdtype) if tdtype != torch.float32 else net
+    if tdtype != torch.float32:
+        if hasattr(net, "activation_dtype"):
+            net.activation_dtype = tdtype    # fp32 parameters, bf16 tensors between the body's kernels
+        else:
+            net = net.to(tdtype)
+    return net
 
 
 def time_model(R, workload, dtype="fp32", target_ms=1500.0):

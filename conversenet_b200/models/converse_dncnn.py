@@ -8,7 +8,11 @@ class ConverseDnCNN(nn.Module):
     """1x1 head (in->64), 20 ConverseBlocks (k=7, padding 6, circular), 1x1 tail.
 
     As in the reference the body always has 20 blocks: `num_blocks` is accepted and
-    ignored (`models/converse_dncnn.py:24`)."""
+    ignored (`models/converse_dncnn.py:24`).
+
+    `activation_dtype` (not in the reference; None = the input's dtype): with torch.bfloat16 the
+    parameters stay fp32 and the tensors between the kernels of the body are bf16 (spectra and
+    accumulation fp32), which halves the body's memory traffic; head and tail run in fp32."""
 
     def __init__(self, in_channels=1, kernel_size=7, num_features=64, padding=6, padding_mode="circular",
                  eps=1e-5, num_blocks=20):
@@ -24,6 +28,11 @@ class ConverseDnCNN(nn.Module):
                                                     padding=padding, padding_mode=padding_mode, eps=1e-5)
                                       for _ in range(20)])
         self.m_tail = nn.Sequential(nn.Conv2d(num_features, in_channels, 1, 1, 0))
+        self.activation_dtype = None
 
     def forward(self, x):
-        return self.m_tail(self.m_body(self.m_head(x)))
+        if self.activation_dtype is None:
+            return self.m_tail(self.m_body(self.m_head(x)))
+        w = self.m_head[0].weight.dtype
+        y = self.m_body(self.m_head(x.to(w)).to(self.activation_dtype))
+        return self.m_tail(y.to(w)).to(x.dtype)

@@ -88,14 +88,15 @@ def test_network_at_benchmark_resolution(fx, case, pset):
 
 
 def test_dncnn_bf16_at_benchmark_resolution(fx):
-    """bf16 tensors end to end (parameters, activations between kernels; spectra and accumulation fp32).
-    Twenty blocks each round their 64-channel stream and 128-channel branch tensors to bf16 (2^-9 per
-    rounding), so the network-level distance is several times the single-layer bar of 5e-3."""
+    """bf16 tensors between the kernels of the body (`activation_dtype`), fp32 parameters, spectra and
+    accumulation: the bar is the bf16 tolerance of the operator, 5e-3 (measured 2.7e-3)."""
     name, wl, ckpt, seed = CASES[0]
     x, extra = bench.synthetic_batch(wl, 1, 700 + seed)
-    m = _network(name, "ckpt", ckpt, seed)
-    out = _run(m, x, extra, torch.bfloat16)
+    m = _network(name, "ckpt", ckpt, seed).cuda()
+    m.activation_dtype = torch.bfloat16
+    with torch.no_grad():
+        out = m(torch.from_numpy(x).cuda().bfloat16()).float().cpu().numpy()
     st = int(fx["stride"])
     err = orc.rel_l2(out[..., ::st, ::st], fx["dncnn_ckpt_bf16_sub"])
-    print("dncnn bf16: rel L2 vs reference (bf16-rounded input and output) %.2e" % err)
-    assert err <= 3e-2
+    print("dncnn bf16 activations: rel L2 vs reference (bf16-rounded input and output) %.2e" % err)
+    assert err <= 5e-3
