@@ -845,6 +845,27 @@ def run_ours(args):
     R.close()
 
 
+def profile_model(args):
+    """Two forwards of one network workload (the first builds tables and workspaces), nothing timed:
+    the command a profiler wraps."""
+    import torch
+    R = Ranks()
+    name = args.profile_model
+    mc = MODEL_CFG[name]
+    tdtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    net = product_network(name, R.dev, tdtype)
+    x, extra = synthetic_batch(name, mc["batch"] if not name.startswith("usrnet") else 4, 100)
+    xs = [torch.from_numpy(x).to(R.dev).to(tdtype)]
+    if extra:
+        xs += [torch.from_numpy(extra[0]).to(R.dev), extra[1]]
+    with torch.no_grad():
+        for _ in range(2):
+            y = net(*xs)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_model": name, "out_shape": list(y.shape), "finite": bool(torch.isfinite(y).all())}))
+    R.close()
+
+
 def read_traffic():
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
     try:
@@ -868,11 +889,15 @@ def main():
                     help="length of the timed region of the headline layer (blocks of --steps steps are repeated)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and library baselines")
+    ap.add_argument("--profile-model", default="",
+                    help="run only two forwards of one network workload at its benchmark batch (profiler runs)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the headline layer's device-timed part (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.profile_model:
+        profile_model(args)
     else:
         run_ours(args)
 

@@ -11,8 +11,15 @@
 namespace cvb {
 namespace gd {
 
+// Two blocks share an SM while the constant operand is small (R0 <= 96: 96 registers per thread);
+// above that one block fills the SM's shared memory and may use the registers of two.
+#if CVB_G0 <= 96
+#define CVB_GD_MIN_BLOCKS 2
+#else
+#define CVB_GD_MIN_BLOCKS 1
+#endif
 template <int R0, int MODE, typename IO>
-__global__ void __launch_bounds__(kThreads, 2) gd_kernel(const Params P) {
+__global__ void __launch_bounds__(kThreads, CVB_GD_MIN_BLOCKS) gd_kernel(const Params P) {
   extern __shared__ unsigned char gd_smem[];
   body<R0, MODE, IO>(P, gd_smem);
 }
