@@ -12,10 +12,10 @@ answered as  solve(x, nearest(x)) + T(d),  d = x0 - nearest(x), with
     T(d) = d - corr(K, zero_insert_s(q)),   q = IFFT2( FFT2(decimate_s(K * d)) / (alias mean |FK|^2 + lambda) )
 (`models/util_converse.py:178-187` with x = 0): the two FFTs are the forward kernel at scale 1 with the
 table of `cvb_build_x0_table`, the k x k correlations are PyTorch convolutions.
-Differentiable as the reference's op is (CompositeImplicitAutograd there):
-dL/dx through the native kernels with `x0` tied to `x` (the gradient returned for `x0` is zero, so the
-chain through `x0 = interpolate(x)` adds nothing twice), parameter gradients through the `torch.fft`
-restatement in `conversenet_b200/autograd.py`.
+Differentiable as the reference's op is (CompositeImplicitAutograd there): separate partial derivatives
+for `x` and `x0` through the native kernels (see `_backward`), parameter gradients through the `torch.fft`
+restatement in `conversenet_b200/autograd.py`.  Deciding whether `x0` equals the up-sampled `x` takes one
+device comparison (a synchronisation) per forward call unless the two are the same tensor at scale 1.
 
 Do not import this module in a process that also loads the reference's own extension:
 a schema can be defined once.
@@ -105,19 +105,31 @@ def _setup_context(ctx, inputs, output):
     x, x0, weight, bias, scale, eps = inputs
     ctx.save_for_backward(x, weight, bias)
     ctx.cfg = (int(scale), float(eps))
-    ref = x if int(scale) == 1 else F.interpolate(x, scale_factor=int(scale), mode="nearest")
-    ctx.tied = bool(torch.equal(x0, ref))
 
 
 def _backward(ctx, g):
+    """True partial derivatives.  The op is out = (F - T N) x + T x0 with F the fused operator for
+    x0 = N x (N = nearest up-sampling) and T the self-adjoint x0-term operator of `_x0_term`:
+        dL/dx0 = T g,      dL/dx = F^T g - N^T (T g),
+    so that x0 = interpolate(x) in the caller's graph adds N^T (T g) back and x receives F^T g in total,
+    while a detached or independent x0 gets exactly its own share.  Parameter gradients go through the
+    `torch.fft` restatement and are written for the tied case (x0 = N x), the only one the reference's
+    module produces."""
     from .autograd import grad_input, spectral_forward
     x, weight, bias = ctx.saved_tensors
     scale, eps = ctx.cfg
-    if not ctx.tied:
-        raise NotImplementedError("converse2d.forward: the backward is written for x0 = nearest-upsample(x)")
-    gx = gw = gb = None
-    if ctx.needs_input_grad[0]:
-        gx = grad_input(g, weight, bias, scale, 0, "circular", eps, x.shape)
+    gx = gx0 = gw = gb = None
+    if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+        B, C, h, w = x.shape
+        k = weight.size(-1)
+        wf = weight.detach().reshape(C, k, k).to(torch.float32).contiguous()
+        tg = _x0_term(g.float().contiguous(), weight, bias, wf, scale, eps, h, w)
+        if ctx.needs_input_grad[1]:
+            gx0 = tg.to(g.dtype)
+        if ctx.needs_input_grad[0]:
+            gx = grad_input(g, weight, bias, scale, 0, "circular", eps, x.shape)
+            back = tg if scale == 1 else F.avg_pool2d(tg, scale) * float(scale * scale)
+            gx = gx - back.to(gx.dtype)
     if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
         with torch.enable_grad():
             w_ = weight.detach().float().requires_grad_(True)
@@ -126,7 +138,6 @@ def _backward(ctx, g):
             gw, gb = torch.autograd.grad(out, (w_, b_), g.float())
         gw = gw.to(weight.dtype) if ctx.needs_input_grad[2] else None
         gb = gb.to(bias.dtype) if ctx.needs_input_grad[3] else None
-    gx0 = torch.zeros_like(g) if ctx.needs_input_grad[1] else None
     return gx, gx0, gw, gb, None, None
 
 

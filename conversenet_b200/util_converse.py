@@ -16,6 +16,21 @@ from . import functional as CF
 BLOCK_FUSION = True
 
 
+class _exact_fp32:
+    """PyTorch's 1x1 convolutions (cuDNN / cuBLAS) in full fp32 for a block of code.  The unfused route of
+    ConverseBlock (channel counts other than 64, or autograd) must hold the operator's 1e-4 bar, which
+    TF32 (10-bit mantissa, on by default for cuDNN convolutions) does not."""
+
+    def __enter__(self):
+        self.saved = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+        torch.backends.cudnn.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_tf32 = False
+
+    def __exit__(self, *exc):
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = self.saved
+        return False
+
+
 class LayerNorm(nn.Module):
     """channels_last / channels_first LayerNorm (`models/util_converse.py:42-68`)."""
 
@@ -187,8 +202,9 @@ class ConverseBlock(nn.Module):
     def forward(self, x):
         if self._fusable(x):
             return self._forward_fused(x)
-        x = self._branch1(x) + x
-        x = self.conv2(x) + x
+        with _exact_fp32():
+            x = self._branch1(x) + x
+            x = self.conv2(x) + x
         return x
 
 
@@ -204,6 +220,7 @@ class ConverseBlockAlphaVariant(ConverseBlock):
     def forward(self, x):
         if self._fusable(x):
             return self._forward_fused(x, self.alpha1, self.alpha2)
-        x = self.alpha1 * self._branch1(x) + x
-        x = self.alpha2 * self.conv2(x) + x
+        with _exact_fp32():
+            x = self.alpha1 * self._branch1(x) + x
+            x = self.alpha2 * self.conv2(x) + x
         return x

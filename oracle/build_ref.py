@@ -21,8 +21,13 @@ OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "converse2d_ref.so")
 
 
+def default_reference_root():
+    """The reference checkout: CONVERSE_REFERENCE_ROOT, else a directory `reference` beside this repository."""
+    return os.environ.get("CONVERSE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def build_ref(reference_root=None, force=False):
-    root = reference_root or os.environ.get("CONVERSE_REFERENCE_ROOT", "/root/reference")
+    root = reference_root or default_reference_root()
     src = os.path.join(root, "Converse2D", "torch_converse2d", "converse2d.cpp")
     if not os.path.exists(src):
         return OUT if os.path.exists(OUT) else None

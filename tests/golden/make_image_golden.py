@@ -11,7 +11,9 @@ import types
 
 import numpy as np
 
-REF = os.environ.get("CONVERSE_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("CONVERSE_REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set CONVERSE_REFERENCE_ROOT to the reference checkout")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

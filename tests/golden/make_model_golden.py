@@ -15,7 +15,9 @@ import numpy as np
 import torch
 
 sys.dont_write_bytecode = True
-REF = os.environ.get("CONVERSE_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("CONVERSE_REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set CONVERSE_REFERENCE_ROOT to the reference checkout")
 sys.path.insert(0, REF)
 from models.converse_dncnn import ConverseDnCNN  # noqa: E402
 from models.converse_srresnet import ConverseMSRResNet  # noqa: E402

@@ -193,3 +193,30 @@ def test_registered_op_is_differentiable_through_x_and_x0():
     rx = torch.autograd.grad(ref.square().mean(), x64)[0]
     assert float((out.detach().double() - ref).norm() / ref.norm()) <= 1e-4
     assert float((gx.double() - rx).norm() / rx.norm()) <= 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scale", [1, 2])
+def test_registered_op_partial_gradients_with_independent_x0(scale):
+    """x0 that is NOT the up-sampled x (the raw op accepts it, `converse2d.cpp:165,193`): the gradients of x
+    and of x0 are separate partial derivatives, checked against fp64 autograd of the torch.fft restatement
+    of the reference's solve (oracle/ref_networks.py)."""
+    import conversenet_b200.torch_converse2d  # noqa: F401  (registers the op)
+    from oracle import ref_networks as rn
+    torch.manual_seed(9)
+    B, C, h, w, k = 2, 3, 20, 24, 5
+    weight = torch.softmax(torch.randn(1, C, k * k, device="cuda"), -1).view(1, C, k, k)
+    bias = torch.randn(1, C, 1, 1, device="cuda") * 0.3
+    x = torch.randn(B, C, h, w, device="cuda", requires_grad=True)
+    x0 = torch.randn(B, C, scale * h, scale * w, device="cuda", requires_grad=True)
+    out = torch.ops.converse2d.forward(x, x0, weight, bias, scale, 1e-5)
+    gx, gx0 = torch.autograd.grad(out.square().mean(), (x, x0))
+    x64 = x.detach().double().requires_grad_(True)
+    x064 = x0.detach().double().requires_grad_(True)
+    lam = torch.sigmoid(bias.double() - 9.0) + 1e-5
+    ref = rn.solve(x64, x064, weight.double(), lam, scale)
+    rx, rx0 = torch.autograd.grad(ref.square().mean(), (x64, x064))
+    rel = lambda a, r: float((a.detach().double() - r).norm() / r.norm())
+    assert rel(out, ref) <= 1e-4
+    assert rel(gx, rx) <= 1e-4
+    assert rel(gx0, rx0) <= 1e-4

@@ -7,7 +7,7 @@ from oracle import converse2d_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-TOL_FP32 = 1e-4   # relative L2, fp32 (the bar BASELINE.json's north_star states)
+TOL_FP32 = 1e-4   # relative L2, fp32: the stated bar of this operator against the reference's torch.fft path
 TOL_BF16 = 5e-3   # relative L2, bf16 I/O with fp32 spectra
 
 
@@ -47,7 +47,7 @@ def test_golden_cases_forced_runtime_plan(golden, i):
 
 
 CONFIGS = {
-    # BASELINE.json configs[0] and configs[1] (full size), SRResNet-style layers reduced in batch
+    # the two single-layer benchmark configurations at full size, SRResNet-style layers reduced in batch
     "cfg1": dict(B=1, C=64, H=128, W=128, k=5, s=1, p=2, mode="circular", eps=1e-5),
     "cfg2": dict(B=16, C=64, H=64, W=64, k=5, s=2, p=2, mode="circular", eps=1e-5),
     "srres_body": dict(B=2, C=128, H=128, W=128, k=5, s=1, p=4, mode="replicate", eps=1e-5),
@@ -57,7 +57,7 @@ CONFIGS = {
 
 
 LARGE = {
-    # planes that take the multi-pass path (workspace): model layers of BASELINE.json configs 3-5, batch reduced
+    # planes that take the multi-pass path (workspace): layers of the three benchmark networks, batch reduced
     "dncnn_body_268": dict(B=2, C=8, H=256, W=256, k=7, s=1, p=6, mode="circular", eps=1e-5),
     "srres_264": dict(B=2, C=6, H=256, W=256, k=5, s=1, p=4, mode="replicate", eps=1e-5),
     "srres_up2_260": dict(B=2, C=4, H=256, W=256, k=2, s=2, p=2, mode="replicate", eps=1e-3),
