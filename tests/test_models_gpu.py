@@ -152,3 +152,22 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
     torch.backends.cudnn.allow_tf32 = False
     want = torch.nn.functional.gelu(conv(xn))
     assert float((out - want).norm() / want.norm()) <= 5e-6
+
+
+def test_graphed_forward_replays_the_eager_result():
+    """One CUDA-graph launch per forward (conversenet_b200/graphs.py) must reproduce the eager forward bit for bit,
+    also for a second input copied into the static buffers."""
+    from conversenet_b200.graphs import GraphedForward
+    from conversenet_b200.models import ConverseDnCNN
+    torch.backends.cudnn.allow_tf32 = False
+    torch.manual_seed(11)
+    net = ConverseDnCNN().cuda().eval()
+    x1 = torch.rand(2, 1, 40, 56, device="cuda")
+    x2 = torch.rand(2, 1, 40, 56, device="cuda")
+    with torch.no_grad():
+        want1, want2 = net(x1).clone(), net(x2).clone()
+    g = GraphedForward(net, x1)
+    assert torch.equal(g(x1).clone(), want1)
+    assert torch.equal(g(x2).clone(), want2)
+    with pytest.raises(RuntimeError):
+        g(torch.rand(1, 1, 40, 56, device="cuda"))
