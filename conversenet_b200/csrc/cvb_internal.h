@@ -45,8 +45,8 @@ int launch_ln_pw_gelu_tc(const BlockParams& P, int sms, int* status, cudaStream_
 // tcgen05: out = res + alpha * (W . t + b), 128 -> 64 channels (P.t, P.x = res, P.w_a, P.b_a, P.alpha1)
 int launch_pw_res_tc(const BlockParams& P, int sms, int* status, cudaStream_t st);
 // warp-specialised, double-buffered versions of the two (k_block_tc2.cu)
-int launch_ln_pw_gelu_tc2(const BlockParams& P, int sms, int* status, cudaStream_t st);
-int launch_pw_res_tc2(const BlockParams& P, int sms, int* status, cudaStream_t st);
+int launch_ln_pw_gelu_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
+int launch_pw_res_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
 
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;

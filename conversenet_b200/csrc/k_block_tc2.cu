@@ -1,6 +1,7 @@
 // Warp-specialised tcgen05 kernel for the 1x1 convolutions of ConverseBlock (128-pixel tiles):
 //   MODE 0:  out = GELU( W . LN(x) + b )          K = 64  -> N = 128   (conv1[0..2] and conv2[0..2])
 //   MODE 1:  out = res + alpha * ( W . t + b )    K = 128 -> N = 64    (conv1[5] / conv2[3] + residual)
+// Tensors are fp32 or bf16 (IO); arithmetic, operands and accumulators are the same for both.
 // Roles (288 threads): warps 0-3 produce -- load 32 pixels x 64 channels each, (LayerNorm), split into
 // TF32 hi + lo, write the K-major core-matrix tiles of one 64-channel chunk; warp 8 issues the MMAs
 // (8 K-steps x 3 per chunk) and commits; warps 4-7 consume -- read their 32 TMEM lanes, bias / GELU /
@@ -39,7 +40,16 @@ __device__ __forceinline__ bool t2_wait(uint64_t* bar, uint32_t parity, volatile
   return false;
 }
 
-template <int MODE>
+// four consecutive pixels of one channel: fp32 (16 bytes) or bf16 (8 bytes) tensors, fp32 in registers
+template <typename IO> __device__ __forceinline__ float4 t2_load4(const IO* p);
+template <> __device__ __forceinline__ float4 t2_load4<float>(const float* p) { return *(const float4*)p; }
+template <> __device__ __forceinline__ float4 t2_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *(const uint2*)p;
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xffff0000u));
+}
+
+template <int MODE, typename IO>
 __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams P, int* status) {
   constexpr int K = T2Shape<MODE>::K, N = T2Shape<MODE>::N, CPT = K / kT2Chunk;
   constexpr int B_SBO = 128, B_LBO = (N / 8) * 128, B_KSTEP = 2 * B_LBO;
@@ -102,12 +112,12 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
       const long long pix0 = tile * kT2Tile;
       const int b = (int)(pix0 / P.HW);
       const int p0 = (int)(pix0 - (long long)b * P.HW);
-      const float* src = (const float*)(MODE == 0 ? P.x : P.t) + (size_t)b * K * P.HW + p0 + warp * 32 + q * 4;
+      const IO* src = (const IO*)(MODE == 0 ? P.x : P.t) + (size_t)b * K * P.HW + p0 + warp * 32 + q * 4;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          dst[4 * j + e] = *(const float4*)(src + (size_t)(kc * kT2Chunk + 4 * (cg + 4 * j) + e) * P.HW);
+          dst[4 * j + e] = t2_load4<IO>(src + (size_t)(kc * kT2Chunk + 4 * (cg + 4 * j) + e) * P.HW);
     };
     float4 vn[16];
     if ((long long)blockIdx.x < ntiles) load_chunk(blockIdx.x, 0, vn);
@@ -228,21 +238,22 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
       if (!t2_wait(&tfull[acc], (uint32_t)((it >> 1) & 1), abort_flag)) break;
       tc::fence_after_sync();
       const size_t off = (size_t)b * N * P.HW + p0 + cw * 32 + lane;
-      float* ob = (float*)P.out + off;
-      const float* rb = (const float*)P.x + off;   // residual (MODE 1)
+      IO* ob = (IO*)P.out + off;
+      const IO* rb = (const IO*)P.x + off;   // residual (MODE 1)
 #pragma unroll 1
       for (int c0 = 0; c0 < N; c0 += 32) {
         float a32[32];
         tc::tmem_ld32(tmem + ((uint32_t)(cw * 32) << 16) + (uint32_t)(acc * N + c0), a32);
         if (MODE == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) ob[(size_t)(c0 + j) * P.HW] = gelu_erf(a32[j] + bias[c0 + j]);
+          for (int j = 0; j < 32; ++j) st_io<IO>(ob, (size_t)(c0 + j) * P.HW, gelu_erf(a32[j] + bias[c0 + j]));
         } else {
           float r[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = rb[(size_t)(c0 + j) * P.HW];
+          for (int j = 0; j < 32; ++j) r[j] = ld_io<IO>(rb, (size_t)(c0 + j) * P.HW);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) ob[(size_t)(c0 + j) * P.HW] = fmaf(alpha[c0 + j], a32[j] + bias[c0 + j], r[j]);
+          for (int j = 0; j < 32; ++j)
+            st_io<IO>(ob, (size_t)(c0 + j) * P.HW, fmaf(alpha[c0 + j], a32[j] + bias[c0 + j], r[j]));
         }
       }
       tc::fence_before_sync();
@@ -266,23 +277,23 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
   }
 }
 
-template <int MODE>
+template <int MODE, typename IO>
 static int launch_t2(const BlockParams& P, int sms, int* status, cudaStream_t st) {
   constexpr int K = T2Shape<MODE>::K, N = T2Shape<MODE>::N;
   const size_t smem = (size_t)(4 * kT2AFloats + 2 * N * K + 2 * N) * sizeof(float) + 8 * sizeof(uint64_t) + 64;
-  CVB_CUDA(cudaFuncSetAttribute(tc_pw_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  CVB_CUDA(cudaFuncSetAttribute(tc_pw_kernel<MODE, IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long long ntiles = ((long long)P.B * P.HW) / kT2Tile;
   const int grid = (int)(ntiles < sms ? ntiles : sms);
-  tc_pw_kernel<MODE><<<grid, kT2Threads, smem, st>>>(P, status);
+  tc_pw_kernel<MODE, IO><<<grid, kT2Threads, smem, st>>>(P, status);
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
 
-int launch_ln_pw_gelu_tc2(const BlockParams& P, int sms, int* status, cudaStream_t st) {
-  return launch_t2<0>(P, sms, status, st);
+int launch_ln_pw_gelu_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st) {
+  return io_dtype == CVB_F32 ? launch_t2<0, float>(P, sms, status, st) : launch_t2<0, __nv_bfloat16>(P, sms, status, st);
 }
-int launch_pw_res_tc2(const BlockParams& P, int sms, int* status, cudaStream_t st) {
-  return launch_t2<1>(P, sms, status, st);
+int launch_pw_res_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st) {
+  return io_dtype == CVB_F32 ? launch_t2<1, float>(P, sms, status, st) : launch_t2<1, __nv_bfloat16>(P, sms, status, st);
 }
 
 }  // namespace cvb

@@ -157,7 +157,7 @@ int cvb_pw_res_mlp_fwd(const void* t, const void* x, void* out, const float* w2,
  * One 1x1 convolution of ConverseBlock with its residual on the tensor cores (tcgen05):
  *   out = res + alpha * (W . t + b),  t (B,2C,HW) -> out (B,C,HW); w (C,2C), b (C), alpha (C) or NULL.
  * conv1[5] + first residual (models/util_converse.py:283,291) and conv2[3] + second residual
- * (:288,292).  fp32 only, C = 64, HW a multiple of 128, t 16-byte aligned; otherwise
+ * (:288,292).  fp32 or bf16 tensors, C = 64, HW a multiple of 128, t 16-byte aligned; otherwise
  * CVB_ERR_UNSUPPORTED_SIZE and the caller uses cvb_pw_res_mlp_fwd.
  */
 int cvb_pw_res_fwd(const void* t, const void* res, void* out, const float* w, const float* b,

@@ -154,6 +154,37 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
     assert float((out - want).norm() / want.norm()) <= 5e-6
 
 
+def test_tensor_core_block_kernels_with_bf16_tensors():
+    """The tcgen05 1x1 kernels on bf16 tensors (fp32 arithmetic) against the same ops in fp32 PyTorch on the
+    bf16-rounded inputs; the only difference is the rounding of the stored result (2^-9 relative)."""
+    from conversenet_b200 import functional as CF, _cabi
+    from conversenet_b200.util_converse import LayerNorm
+    torch.backends.cudnn.allow_tf32 = False
+    torch.manual_seed(6)
+    ln = LayerNorm(64, eps=1e-5, data_format="channels_first").cuda()
+    conv = torch.nn.Conv2d(64, 128, 1).cuda()
+    conv2 = torch.nn.Conv2d(128, 64, 1).cuda()
+    with torch.no_grad():
+        ln.weight.add_(0.3 * torch.randn_like(ln.weight))
+        ln.bias.add_(0.2 * torch.randn_like(ln.bias))
+    x = torch.randn(2, 64, 64, 96, device="cuda").bfloat16()
+    t = torch.randn(2, 128, 64, 96, device="cuda").bfloat16()
+    alpha = torch.randn(1, 64, 1, 1, device="cuda")
+    out = CF.ln_pw_gelu(x, ln, conv)
+    got2 = CF.pw_res(t, x, conv2, alpha)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16 and got2.dtype == torch.bfloat16
+    assert _cabi.load().cvb_last_device_status(1) == 0
+    with torch.no_grad():
+        want = torch.nn.functional.gelu(conv(ln(x.float())))
+        want2 = x.float() + alpha * conv2(t.float())
+    assert float((out.float() - want).norm() / want.norm()) <= 4e-3
+    assert float((got2.float() - want2).norm() / want2.norm()) <= 4e-3
+    with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 0):       # the CUDA-core kernel on the same bf16 tensors
+        ref = CF.ln_pw_gelu(x, ln, conv)
+    assert float((out.float() - ref.float()).norm() / ref.float().norm()) <= 4e-3
+
+
 def test_graphed_forward_replays_the_eager_result():
     """One CUDA-graph launch per forward (conversenet_b200/graphs.py) must reproduce the eager forward bit for bit,
     also for a second input copied into the static buffers."""
