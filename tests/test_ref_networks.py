@@ -1,7 +1,8 @@
 """The network restatement in oracle/ref_networks.py (the checker and CPU baseline of the network
 workloads) against the unmodified reference.
 
-Where the reference checkout is present (environment variable CONVERSE_REFERENCE_ROOT) every
+Where the reference checkout is present (environment variable CONVERSE_REFERENCE_ROOT, else a
+directory `reference` beside this repository) every
 restated network must give the reference network's output on CPU with the same state dict (fp64:
 1e-10; fp32: within the reference's own rounding noise).  Everywhere, the restatement must load the reference's trained checkpoints strictly (copies
 under tests/golden/model_zoo) and so must this package's mirrors; and it must reproduce the stored
@@ -47,8 +48,9 @@ def _small_inputs(name):
 
 @pytest.mark.parametrize("name", sorted(CKPT))
 def test_restatement_matches_imported_reference(name):
-    ref_root = os.environ.get("CONVERSE_REFERENCE_ROOT")
-    if not ref_root or not os.path.isdir(ref_root):
+    from oracle.build_ref import default_reference_root
+    ref_root = default_reference_root()
+    if not os.path.isdir(os.path.join(ref_root, "models")):
         pytest.skip("reference checkout not present")
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)

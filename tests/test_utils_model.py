@@ -90,8 +90,9 @@ def test_mode_dispatch_and_bad_mode():
 
 
 def test_against_the_reference_helpers_when_present():
-    ref_root = os.environ.get("CONVERSE_REFERENCE_ROOT", "")
-    if not ref_root or not os.path.isdir(os.path.join(ref_root, "utils")):
+    from oracle.build_ref import default_reference_root
+    ref_root = default_reference_root()
+    if not os.path.isdir(os.path.join(ref_root, "utils")):
         pytest.skip("reference tree not present")
     sys.path.insert(0, ref_root)
     try:
