@@ -33,7 +33,6 @@ struct StripParams {
   int halo_l, halo_r;  // extra columns the epilogue reads left / right of a strip (s > 1)
   int big_y, big_x;    // the column / row plan has a large-prime stage (second tile buffer present)
   RaderInfo ry, rx;
-  const float* dft_matrix;  // tensor-core plans: the constant DFT operand (hi, lo) of the launching kernel's axis
 };
 
 // ---- direct butterfly for a large prime radix, out of place (src -> dst) ----

@@ -14,37 +14,27 @@
 //                     store (s == 1), or tile + upsampling epilogue (s > 1)
 #pragma once
 #include "cvb_strip.cuh"
-#include "cvb_tcdft.cuh"
 
 namespace cvb {
 
-// How a first radix R0 that is a large prime runs: on the tensor cores (cvb_tcdft.cuh) from
-// kTcMinRadix up, where the dense contraction beats the sub-transforms; below, as Rader's
-// algorithm with a compile-time sub-plan (measured on 268 = 67 * 4 and 516 = 43 * 12).
-constexpr int kTcMinRadix = 47;
-CVB_HD constexpr bool strip2_tc(int R0) { return R0 >= kTcMinRadix; }
-CVB_HD constexpr bool strip2_rader(int R0) { return R0 > kMaxRegisterRadix && R0 < kTcMinRadix; }
-// threads per block: the tensor-core plans add the warp that issues the MMAs
-CVB_HD constexpr int strip2_threads(int R0) { return strip2_tc(R0) ? 288 : 256; }
+// A first radix R0 that is a prime beyond the register codelets runs as Rader's algorithm
+// with a compile-time sub-plan (516 = 43 * 12).  (Sizes 4 * R0 with a large R0 do not come
+// here: their first stage is a dense contraction on the tensor cores, cvb_gemmdft.cuh.)
+CVB_HD constexpr bool strip2_rader(int R0) { return R0 > kMaxRegisterRadix; }
+CVB_HD constexpr int strip2_threads(int) { return 256; }
 // lines per strip (columns for A / C, pos_y values for B): the widest of 32 / 16 / 8 whose
-// tile stays under ~76 KB, so that three blocks share an SM; for a plan whose first radix is a
-// large prime (tensor-core stage, cvb_tcdft.cuh) the widest that leaves room for two blocks
-// per SM next to the stage's operands
+// tile stays under ~76 KB, so that three blocks share an SM
 CVB_HD constexpr int strip2_lines(int N, int R0) {
   if (strip2_rader(R0))   // two tile buffers
     return 2 * N * 33 * 8 <= 76 * 1024 ? 32 : 2 * N * 17 * 8 <= 76 * 1024 ? 16 : 8;
-  if (strip2_tc(R0)) {
-    const size_t fixed = tcdft::bytes(R0) + (size_t)N * 8 + 4096, budget = 112 * 1024;
-    return fixed + (size_t)N * 33 * 8 <= budget ? 32 : fixed + (size_t)N * 17 * 8 <= budget ? 16 : 8;
-  }
   return N * 33 * 8 <= 76 * 1024 ? 32 : N * 17 * 8 <= 76 * 1024 ? 16 : 8;
 }
 
-// shared memory (bytes) of one block: tile, twiddles, maps / taps, tensor-core operands
+// shared memory (bytes) of one block: tile, twiddles, maps / taps
 CVB_HD size_t strip2_smem(int N, int lines, int R0, int k) {
   const size_t f2 = (size_t)(strip2_rader(R0) ? 2 : 1) * N * (lines | 1) + N + (N + lines + 1) / 2 +
                     (k * k + 1) / 2 + (strip2_rader(R0) ? rader_floats2(R0) : 0);
-  return f2 * sizeof(float2) + (strip2_tc(R0) ? tcdft::bytes(R0) + 128 : 0);
+  return f2 * sizeof(float2);
 }
 
 // ---- Rader stage with a compile-time sub-plan R - 1 = S0 * S1, gather and scatter fused ----
@@ -363,7 +353,6 @@ struct Strip2Smem {
   int* rmap;
   int* cmap;
   float* wk;
-  void* tc;      // tensor-core operands (128-byte aligned)
 };
 CVB_HD Strip2Smem strip2_carve(float2* smem, int N, int lines, int k, int R0) {
   const int tp = lines | 1;
@@ -376,31 +365,8 @@ CVB_HD Strip2Smem strip2_carve(float2* smem, int N, int lines, int k, int R0) {
   m.rmap = (int*)(m.rtab + (rad ? rader_floats2(R0) : 0));
   m.cmap = m.rmap + N;
   m.wk = (float*)((float2*)m.rmap + (N + lines + 1) / 2);
-  m.tc = (void*)(((uintptr_t)(m.wk + 2 * ((k * k + 1) / 2)) + 127) & ~(uintptr_t)127);
   return m;
 }
-
-// Phase clocks of the large-prime kernels, for tuning builds only (-DCVB_PHASE_CLOCK): thread 0 of
-// every block adds the cycles since its previous tick to slot i of a device array.
-#if defined(CVB_PHASE_CLOCK) && defined(__CUDA_ARCH__)
-extern __device__ unsigned long long g_phase_cycles[32];
-#define CVB_TICK_INIT() long long tick_prev_ = clock64()
-#define CVB_TICK(i)                                                              \
-  do {                                                                           \
-    if (threadIdx.x == 0) {                                                      \
-      const long long now_ = clock64();                                          \
-      atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - tick_prev_));    \
-      tick_prev_ = now_;                                                         \
-    }                                                                            \
-  } while (0)
-#else
-#define CVB_TICK_INIT() do { } while (0)
-#define CVB_TICK(i) do { } while (0)
-#endif
-
-// one large-prime stage over the whole tile (all threads on the GPU; plain loops on the host)
-#define CVB_TC_STAGE(R, R1_, LN_, ctx, cur, tp, tw, pre_, osg_) \
-  tcdft::stage<R, R1_, LN_>(ctx, cur, tp, tw, pre_, osg_, nthr_emu)
 
 // ---- A: column strip forward ----
 template <typename IO, int R0, int R1, int S0, int S1>
@@ -426,30 +392,13 @@ __host__ __device__ void strip2_A_body(const StripParams& SP, int lp, int strip,
   if constexpr (!big) {
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h), strip_maps(tid, nthr, m.rmap, m.cmap, x0, nc, P)));
     CVB_PHASE((fft_pass<R0, IO, h, h, R1, 0, PASS_SRC_GLOBAL>(tid, nthr, a0, io, 0)));
-  } else if constexpr (strip2_rader(R0)) {
+  } else {
     const RaderSmem rsm = rader_views(m.rtab, R0);
     CVB_PHASE(strip_maps(tid, nthr, m.rmap, m.cmap, x0, nc, P));
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
                copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, rader_floats2(R0)),
                tile_load_maps<IO, LN, (h * LN + 255) / 256>(tid, nthr, m.cur, tp, nc, h, m.rmap, m.cmap, io)));
     CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, false, 1.0f);
-  } else {
-    CVB_TICK_INIT();
-    tcdft::Ctx tcx = tcdft::carve<R0>(m.tc, P.status);
-    tcdft::setup<R0>(tcx, SP.dft_matrix);
-    CVB_TICK(0);
-    CVB_PHASE(strip_maps(tid, nthr, m.rmap, m.cmap, x0, nc, P));
-    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
-               tile_load_maps<IO, LN, (h * LN + 255) / 256>(tid, nthr, m.cur, tp, nc, h, m.rmap, m.cmap, io)));
-    CVB_TICK(1);
-    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, false, 1.0f);
-    CVB_TICK(2);
-    CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
-    CVB_TICK(3);
-    CVB_PHASE(tileT_to_ws<h>(tid, nthr, m.cur, tp, nc, ST, x0));
-    tcdft::finish<R0>(tcx);
-    CVB_TICK(4);
-    return;
   }
   CVB_PHASE((fft_pass<R1, IO, h, R1, 1, 0, 0>(tid, nthr, a1, io, 0)));
   CVB_PHASE(tileT_to_ws<h>(tid, nthr, m.cur, tp, nc, ST, x0));
@@ -484,7 +433,7 @@ __host__ __device__ void strip2_B_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((fft_pass<R0, float, w, w, R1, 0, PASS_SRC_WS>(tid, nthr, a0, io, 0)));
     CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
     CVB_PHASE((fft_pass<R0, float, w, w, R1, 0, PASS_PRE | PASS_DST_WS>(tid, nthr, a0, io, 0)));
-  } else if constexpr (strip2_rader(R0)) {
+  } else {
     const RaderSmem rsm = rader_views(m.rtab, R0);
     CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob + h, w),
                copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.rx.off, rader_floats2(R0)),
@@ -493,22 +442,6 @@ __host__ __device__ void strip2_B_body(const StripParams& SP, int lp, int strip,
     CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
     CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.rx, rsm, true, 1.0f);
     CVB_PHASE(tile_rows_to_ws2<LN>(tid, nthr, m.cur, tp, w, nc, ST, h, y0));
-  } else {
-    CVB_TICK_INIT();
-    tcdft::Ctx tcx = tcdft::carve<R0>(m.tc, P.status);
-    tcdft::setup<R0>(tcx, SP.dft_matrix);
-    CVB_TICK(8);
-    CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob + h, w), tile_rows_from_ws2<LN, (w * LN + 255) / 256>(tid, nthr, m.cur, tp, w, nc, ST, h, y0)));
-    CVB_TICK(9);
-    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, false, 1.0f);
-    CVB_TICK(10);
-    CVB_PHASE((fft_pass<R1, float, w, R1, 1, 0, PASS_MID>(tid, nthr, a1, io, 0)));
-    CVB_TICK(11);
-    CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, true, 1.0f);
-    CVB_TICK(12);
-    CVB_PHASE(tile_rows_to_ws2<LN>(tid, nthr, m.cur, tp, w, nc, ST, h, y0));
-    tcdft::finish<R0>(tcx);
-    CVB_TICK(13);
   }
 }
 
@@ -536,9 +469,7 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
   const PassArgs a0 = strip_pass(m.cur, tp, nt, h, h, R1, m.tw);
   const PassArgs a1 = strip_pass(m.cur, tp, nt, h, R1, 1, m.tw);
   const float* gw = P.weight + (size_t)c * P.k * P.k;
-  constexpr bool tcs = strip2_tc(R0), rad = strip2_rader(R0);
-  tcdft::Ctx tcx = tcdft::carve<tcs ? R0 : 3>(m.tc, P.status);
-  if constexpr (tcs) tcdft::setup<R0>(tcx, SP.dft_matrix);
+  constexpr bool rad = strip2_rader(R0);
   CVB_PHASE((copy_twiddles(tid, nthr, m.tw, blob, h),
              copy_twiddles(tid, nthr, m.rtab, blob + h + w + SP.ry.off, rad ? rader_floats2(R0) : 0),
              copy_floats(tid, nthr, m.wk, gw, P.s > 1 ? P.k * P.k : 0),
@@ -552,18 +483,13 @@ __host__ __device__ void strip2_C_body(const StripParams& SP, int lp, int strip,
       CVB_PHASE(tile_epilogue<IO>(tid, nthr, m.cur, tp, nc, x0, hl, m.wk, P, io));
     }
   } else {
-    if constexpr (rad) {
-      const RaderSmem rsm = rader_views(m.rtab, R0);
-      CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, true, -1.0f);
-    } else {
-      CVB_TC_STAGE(R0, R1, LN, tcx, m.cur, tp, m.tw, true, -1.0f);
-    }
+    const RaderSmem rsm = rader_views(m.rtab, R0);
+    CVB_RADER_STATIC(R0, R1, S0, S1, m.cur, m.oth, a0, SP.ry, rsm, true, -1.0f);
     if (P.s == 1) {
       CVB_PHASE((tile_store_crop2<IO, LN>(tid, nthr, m.cur, tp, nc, x0, P, io)));
     } else {
       CVB_PHASE(tile_epilogue<IO>(tid, nthr, m.cur, tp, nc, x0, hl, m.wk, P, io));
     }
-    if constexpr (tcs) tcdft::finish<R0>(tcx);
   }
 }
 

@@ -9,18 +9,6 @@
 #define CVB_CAT_(n, a, b) launch_strip2##n##_##a##_##b
 #define CVB_CAT(n, a, b) CVB_CAT_(n, a, b)
 
-#ifdef CVB_PHASE_CLOCK
-namespace cvb { __device__ unsigned long long g_phase_cycles[32]; }
-extern "C" int cvb_debug_phase_cycles(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, cvb::g_phase_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
-  if (reset) {
-    unsigned long long z[32] = {0};
-    if (cudaMemcpyToSymbol(cvb::g_phase_cycles, z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
-
 namespace cvb {
 
 constexpr int kLines = strip2_lines(CVB_R0 * CVB_R1, CVB_R0);
@@ -44,45 +32,9 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) strip2_C_kernel(const St
 }
 
 namespace {
-constexpr bool kBig = strip2_tc(CVB_R0);   // this plan's first stage runs on the tensor cores
-// Constant operand of the tensor-core stage (hi and lo halves of the DFT matrix in operand
-// layout): a fixed array in the library image, filled by one small kernel the first time a
-// device runs this plan (stream-ordered before the first user), copied into shared memory by
-// every block.
-__device__ __align__(16) float g_dft_matrix[kBig ? 2 * tcdft::Geo<kBig ? CVB_R0 : 3>::B_FLOATS : 4];
-
-int dft_matrix_ready(const float** out, cudaStream_t st) {
-  *out = nullptr;
-  if (!kBig) return CVB_OK;
-  static bool done[64] = {false};
-  static float* addr[64] = {nullptr};
-  int dev = 0;
-  CVB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return CVB_ERR_BAD_ARGUMENT;
-  if (!done[dev]) {
-    void* p = nullptr;
-    CVB_CUDA(cudaGetSymbolAddress(&p, g_dft_matrix));
-    addr[dev] = (float*)p;
-    tcdft::dft_matrix_kernel<kBig ? CVB_R0 : 3><<<8, 256, 0, st>>>(addr[dev]);
-    CVB_CUDA(cudaGetLastError());
-    // Other streams may use the array from the next call on: finish the fill now.  Inside a
-    // stream capture nothing can be waited for, so the fill stays part of every captured call.
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    CVB_CUDA(cudaStreamIsCapturing(st, &cap));
-    if (cap == cudaStreamCaptureStatusNone) {
-      CVB_CUDA(cudaStreamSynchronize(st));
-      done[dev] = true;
-    }
-  }
-  *out = addr[dev];
-  return CVB_OK;
-}
-
 template <typename K>
 int launch_k(K kernel, const StripParams& SP0, int nstrips, size_t smem, cudaStream_t st) {
-  StripParams SP = SP0;
-  const int rc = dft_matrix_ready(&SP.dft_matrix, st);
-  if (rc != CVB_OK) return rc;
+  const StripParams& SP = SP0;
   CVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kernel<<<dim3(nstrips, SP.npair), kThreads, smem, st>>>(SP);
   CVB_CUDA(cudaGetLastError());

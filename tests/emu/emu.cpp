@@ -125,7 +125,6 @@ int emu_converse2d_strip(const float* x, float* out, const void* table, const fl
   std::vector<float2> ws((size_t)g.chunk_pairs * P.h * P.w);
   std::vector<float2> smem((g.smem_col > g.smem_row ? g.smem_col : g.smem_row) / sizeof(float2) + 16);
   StripParams SP;
-  SP.dft_matrix = nullptr;
   SP.f = P; SP.ws = ws.data(); SP.cw = g.cw; SP.rh = g.rh; SP.halo_l = g.halo_l; SP.halo_r = g.halo_r;
   SP.big_y = plan_has_big(P.py) ? 1 : 0; SP.big_x = plan_has_big(P.px) ? 1 : 0;
   rader_both(P.py, P.px, SP.ry, SP.rx);
@@ -160,7 +159,6 @@ int emu_converse2d_strip2(const float* x, float* out, const void* table, const f
   std::vector<float2> ws((size_t)2 * P.h * P.w);
   std::vector<float2> smem((strip2_smem(128, 32, 127, k) + strip2_smem(128, 32, 43, k)) / sizeof(float2) + 64);
   StripParams SP;
-  SP.dft_matrix = nullptr;
   SP.f = P; SP.ws = ws.data(); SP.cw = g.cw; SP.rh = g.rh; SP.halo_l = g.halo_l; SP.halo_r = g.halo_r;
   SP.big_y = plan_has_big(P.py) ? 1 : 0; SP.big_x = plan_has_big(P.px) ? 1 : 0;
   rader_both(P.py, P.px, SP.ry, SP.rx);
@@ -170,9 +168,6 @@ int emu_converse2d_strip2(const float* x, float* out, const void* table, const f
   } else if (P.h == 58 && P.w == 86) {
     run_strip2(SP, npairs, 2, smem, nthr, strip2_A_body<float, 29, 2, 7, 4>, strip2_B_body<43, 2, 7, 6>,
                strip2_C_body<float, 29, 2, 7, 4>, strip2_lines(58, 29), strip2_lines(86, 43));
-  } else if (P.h == 94 && P.w == 106) {   // first radices 47 and 53: the tensor-core stage's host stand-in
-    run_strip2(SP, npairs, 2, smem, nthr, strip2_A_body<float, 47, 2, 0, 0>, strip2_B_body<53, 2, 0, 0>,
-               strip2_C_body<float, 47, 2, 0, 0>, strip2_lines(94, 47), strip2_lines(106, 53));
   } else {
     return -100;
   }

@@ -117,8 +117,6 @@ def test_emu_strip_path_large_primes(emu, shape, k, s, p, mode):
     ((2, 1, 30, 38), 3, 2, 2, "circular"),    # upsampling epilogue with halo columns
     ((3, 1, 54, 82), 5, 1, 2, "reflect"),     # 58 x 86: Rader first stages (29, 43)
     ((1, 2, 54, 82), 2, 2, 2, "replicate"),
-    ((2, 1, 90, 102), 5, 1, 2, "circular"),   # 94 x 106: first radices 47, 53 as tensor-core GEMMs (host stand-in)
-    ((1, 1, 90, 102), 3, 2, 2, "replicate"),
 ])
 def test_emu_strip_compile_time_axis_plans(emu, shape, k, s, p, mode):
     rng = np.random.default_rng(23)
