@@ -867,7 +867,8 @@ def profile_model(args):
     mc = MODEL_CFG[name]
     tdtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
     net = product_network(name, R.dev, tdtype)
-    x, extra = synthetic_batch(name, mc["batch"] if not name.startswith("usrnet") else 4, 100)
+    batch = args.profile_batch or (mc["batch"] if not name.startswith("usrnet") else 4)
+    x, extra = synthetic_batch(name, batch, 100)
     xs = [torch.from_numpy(x).to(R.dev).to(tdtype)]
     if extra:
         xs += [torch.from_numpy(extra[0]).to(R.dev), extra[1]]
@@ -904,6 +905,8 @@ def main():
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and library baselines")
     ap.add_argument("--profile-model", default="",
                     help="run only two forwards of one network workload at its benchmark batch (profiler runs)")
+    ap.add_argument("--profile-batch", type=int, default=0,
+                    help="batch of the --profile-model forwards (default: the workload's per-GPU batch)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the headline layer's device-timed part (for profiler runs)")
     args = ap.parse_args()

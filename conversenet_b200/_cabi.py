@@ -38,6 +38,9 @@ SIGNATURES = {
     "cvb_pw_res_fwd": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 4 + [_c.c_void_p]),
     "cvb_plan_radices": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int), _c.c_int]),
     "cvb_fits_shared": (_c.c_int, [_c.c_int, _c.c_int]),
+    "cvb_cross_spectrum": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 7 + [_c.c_void_p]),
+    "cvb_cross_spectrum_supported": (_c.c_int, [_c.c_int, _c.c_int]),
+    "cvb_tap_gradient": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 8 + [_c.c_void_p]),
 }
 
 _lib = None

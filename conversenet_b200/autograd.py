@@ -18,14 +18,26 @@ the operator is linear in x.  Its adjoint, applied to g = dL/dout, is
 The two FFTs and the multiply are the forward kernel itself (scale 1, no padding) run with the
 conjugated transfer table; u, v and the padding adjoint are small PyTorch tensor ops.
 
-dL/dweight and dL/dbias go through the table (P depends on K and lambda) and are not
-written natively: when a parameter requires a gradient they come from autograd through a
-`torch.fft` restatement of the same closed form (`spectral_forward`, library kernels).
+dL/dweight and dL/dbias.  The parameters act through the multiplier M (G or P, one (C,h,w) complex
+tensor) and, at scale >= 2, through the taps of the epilogue's correlation:
+    L = (1 / (h w)) Re sum_f M[f] D[f]  (+ terms without M),
+    D[f] = sum_b FFT2(y_b)[f] conj(FFT2(q_b)[f]),   q = g_full (scale 1) or v (scale >= 2).
+D, the reduction over the batch, is one native kernel (`functional.cross_spectrum`); the chain rule
+from D to the k x k taps and lambda runs through `transfer_multiplier`, the closed form of M written
+with `torch.fft` on that single (C, s h, s w) tensor.  The direct tap term of scale >= 2,
+dK[a] = sum_m g_full[s m - a + c] r[m], needs r = IFFT2(P . FFT2(y)): the forward kernel at scale 1
+on the padded planes, followed by k^2 strided products.  Planes the cross-spectrum kernel does not
+take (two planes must fit shared memory) fall back to autograd through `spectral_forward`, the
+whole operator restated with `torch.fft` (library kernels).
 """
 import torch
 import torch.nn.functional as F
 
 from . import functional as CF
+
+
+# False: parameter gradients always take the `spectral_forward` route (tests compare the two)
+NATIVE_PARAM_GRADS = True
 
 
 def _pad(x, p, mode):
@@ -36,34 +48,44 @@ def _pad(x, p, mode):
     return F.pad(x, (p, p, p, p), mode=mode)
 
 
-def spectral_forward(x, weight, bias, scale, padding, padding_mode, eps):
-    """The operator written with `torch.fft` in its collapsed form (differentiable in every
-    argument; any device and float dtype).  Used for parameter gradients and by the tests."""
-    s, p = int(scale), int(padding)
-    B, C, H, W = x.shape
-    k = weight.size(-1)
+def transfer_multiplier(weight, bias, scale, eps, h, w):
+    """The operator's multiplier on the h x w grid, (1,C,h,w) complex, natural frequency order,
+    differentiable in `weight` (1,C,k,k) and `bias` (1,C,1,1): G at scale 1, P at scale >= 2."""
+    s = int(scale)
+    C, k = weight.size(1), weight.size(-1)
     c = k // 2
-    y = _pad(x, p, padding_mode)
-    h, w = y.shape[-2:]
     lam = torch.sigmoid(bias - 9.0) + eps                                    # (1,C,1,1)
     # kernel spectrum on the s*h x s*w grid, kernel centre (k//2, k//2) at the origin
-    psf = torch.zeros(1, C, s * h, s * w, dtype=x.dtype, device=x.device)
+    psf = torch.zeros(1, C, s * h, s * w, dtype=weight.dtype, device=weight.device)
     psf[..., :k, :k] = weight
     psf = torch.roll(psf, shifts=(-c, -c), dims=(-2, -1))
     FK = torch.fft.fft2(psf)
     if s == 1:
-        G = (FK.conj() + lam) / (FK.real ** 2 + FK.imag ** 2 + lam)
-        return torch.fft.ifft2(G * torch.fft.fft2(y)).real[..., p:p + H, p:p + W]
+        return (FK.conj() + lam) / (FK.real ** 2 + FK.imag ** 2 + lam)
     # box factor of the nearest upsampling, alias means over the s x s copies of the h x w spectrum
-    box = torch.zeros(s * h, s * w, dtype=x.dtype, device=x.device)
+    box = torch.zeros(s * h, s * w, dtype=weight.dtype, device=weight.device)
     box[:s, :s] = 1.0
     D = torch.fft.fft2(box)
 
     def alias_mean(Z):
         return Z.reshape(*Z.shape[:-2], s, h, s, w).mean(dim=(-4, -2))
 
-    P = (1.0 - alias_mean(FK * D)) / (alias_mean(FK.real ** 2 + FK.imag ** 2) + lam)
-    r = torch.fft.ifft2(P * torch.fft.fft2(y)).real                           # (B,C,h,w)
+    return (1.0 - alias_mean(FK * D)) / (alias_mean(FK.real ** 2 + FK.imag ** 2) + lam)
+
+
+def spectral_forward(x, weight, bias, scale, padding, padding_mode, eps):
+    """The operator written with `torch.fft` in its collapsed form (differentiable in every
+    argument; any device and float dtype).  Fallback for parameter gradients; used by the tests."""
+    s, p = int(scale), int(padding)
+    B, C, H, W = x.shape
+    k = weight.size(-1)
+    c = k // 2
+    y = _pad(x, p, padding_mode)
+    h, w = y.shape[-2:]
+    M = transfer_multiplier(weight.to(x.dtype), bias.to(x.dtype), s, eps, h, w)
+    if s == 1:
+        return torch.fft.ifft2(M * torch.fft.fft2(y)).real[..., p:p + H, p:p + W]
+    r = torch.fft.ifft2(M * torch.fft.fft2(y)).real                           # (B,C,h,w)
     z = torch.zeros(B, C, s * h, s * w, dtype=x.dtype, device=x.device)
     z[..., ::s, ::s] = r
     # corr(K, z)[i] = sum_a K[a] z[i + a - c], circular
@@ -81,30 +103,41 @@ def _conjugated(table, n_entries):
     return t
 
 
-def grad_input(g, weight, bias, scale, padding, padding_mode, eps, in_shape, table=None):
+class _Cotangent:
+    """g = dL/dout prepared once per backward call: zero-extended to the padded grid (adjoint of the
+    crop) and, at scale >= 2, v[m] = sum_a K[a] g_full[s m - a + c] (adjoint of corr(K, zero_insert(.)):
+    a strided cross-correlation with the flipped kernel).  dL/dx and the parameter gradients share it."""
+
+    def __init__(self, g, wf, k, s, p):
+        ps = p * s
+        self.g_full = (F.pad(g, (ps, ps, ps, ps)) if ps else g).float().contiguous()
+        self.v = None
+        if s > 1:
+            c = k // 2
+            C = wf.size(0)
+            gp = F.pad(self.g_full, (k - 1 - c, c, k - 1 - c, c), mode="circular")
+            self.v = F.conv2d(gp, wf.flip(-2, -1).reshape(C, 1, k, k), stride=s, groups=C).contiguous()
+
+
+def grad_input(g, weight, bias, scale, padding, padding_mode, eps, in_shape, table=None, cot=None):
     """dL/dx for g = dL/dout (B,C,sH,sW) through the native kernels.  `table`: the forward's
     transfer table for the padded size, if the caller has it."""
     s, p = int(scale), int(padding)
     B, C, H, W = in_shape
     h, w = H + 2 * p, W + 2 * p
     k = weight.size(-1)
-    c = k // 2
     if table is None:
         table, _ = CF.build_transfer(weight, bias, s, eps, h, w)
     wf = weight.detach().reshape(C, k, k).to(torch.float32).contiguous()
     ctab = _conjugated(table, C * h * w)
-    g = g.contiguous()
-    ps = p * s
-    g_full = F.pad(g, (ps, ps, ps, ps)) if ps else g                          # zeros outside the crop
+    if cot is None:
+        cot = _Cotangent(g, wf, k, s, p)
     if s == 1:
-        g_y = CF.converse2d_forward(g_full, ctab, wf, k, 1, 0, "circular")
+        g_y = CF.converse2d_forward(cot.g_full, ctab, wf, k, 1, 0, "circular")
     else:
-        u = F.avg_pool2d(g_full.float(), s) * float(s * s)
-        # v[m] = sum_a K[a] g_full[s m - a + c]: a strided cross-correlation with the flipped kernel
-        gp = F.pad(g_full.float(), (k - 1 - c, c, k - 1 - c, c), mode="circular")
-        v = F.conv2d(gp, wf.flip(-2, -1).reshape(C, 1, k, k), stride=s, groups=C)
-        g_y = u + CF.converse2d_forward(v.contiguous(), ctab, wf, k, 1, 0, "circular")
-        g_y = g_y.to(g.dtype)
+        u = F.avg_pool2d(cot.g_full, s) * float(s * s)
+        g_y = u + CF.converse2d_forward(cot.v, ctab, wf, k, 1, 0, "circular")
+    g_y = g_y.to(g.dtype)
     if p == 0:
         return g_y
     # adjoint of the boundary padding: PyTorch's own pad backward (a gather / scatter-add)
@@ -114,8 +147,39 @@ def grad_input(g, weight, bias, scale, padding, padding_mode, eps, in_shape, tab
     return torch.autograd.grad(padded, probe, g_y)[0]
 
 
+def grad_params(x, g, weight, bias, scale, padding, padding_mode, eps, table=None, cot=None):
+    """(dL/dweight, dL/dbias) in fp32 for g = dL/dout, batch reductions in the native kernels; None when
+    the cross-spectrum kernel does not take the padded plane (the caller then falls back)."""
+    s, p = int(scale), int(padding)
+    B, C, H, W = x.shape
+    h, w = H + 2 * p, W + 2 * p
+    if not CF.cross_spectrum_supported(h, w):
+        return None
+    k = weight.size(-1)
+    if table is None:
+        table, _ = CF.build_transfer(weight, bias, s, eps, h, w)
+    wf = weight.detach().reshape(C, k, k).to(torch.float32).contiguous()
+    xf = x.detach().float().contiguous()
+    if cot is None:
+        cot = _Cotangent(g, wf, k, s, p)
+    D = CF.cross_spectrum(xf, cot.g_full if s == 1 else cot.v, table, p, padding_mode)   # (C,h,w) complex
+    with torch.enable_grad():
+        w_ = weight.detach().float().requires_grad_(True)
+        b_ = bias.detach().float().requires_grad_(True)
+        M = transfer_multiplier(w_, b_, s, eps, h, w)[0]
+        proxy = (M * D).real.sum() / float(h * w)
+        gw, gb = torch.autograd.grad(proxy, (w_, b_))
+    if s > 1:
+        # direct dependence of corr(K, zero_insert(r)) on the taps; r = the forward at scale 1 on the padded planes
+        y = _pad(xf, p, padding_mode).contiguous()
+        r = CF.converse2d_forward(y, table, wf, k, 1, 0, "circular")
+        gw = gw + CF.tap_gradient(cot.g_full, r, k, s).reshape(1, C, k, k)
+    return gw, gb
+
+
 class Converse2DFunction(torch.autograd.Function):
-    """Native forward; native dL/dx; parameter gradients through `spectral_forward`."""
+    """Native forward; native dL/dx; parameter gradients from the native batch-summed cross spectrum
+    (`grad_params`), through `spectral_forward` for planes that kernel does not take."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, table, wf, kernel_size, scale, padding, padding_mode, eps):
@@ -129,14 +193,21 @@ class Converse2DFunction(torch.autograd.Function):
         x, weight, bias = ctx.saved_tensors
         k, s, p, mode, eps = ctx.cfg
         gx = gw = gb = None
+        C = weight.size(1)
+        cot = _Cotangent(g, weight.detach().reshape(C, k, k).to(torch.float32), k, s, p)
         if ctx.needs_input_grad[0]:
-            gx = grad_input(g, weight, bias, s, p, mode, eps, x.shape, table=ctx.table)
+            gx = grad_input(g, weight, bias, s, p, mode, eps, x.shape, table=ctx.table, cot=cot)
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
-            with torch.enable_grad():
-                w_ = weight.detach().float().requires_grad_(True)
-                b_ = bias.detach().float().requires_grad_(True)
-                out = spectral_forward(x.detach().float(), w_, b_, s, p, mode, eps)
-                gw, gb = torch.autograd.grad(out, (w_, b_), g.float())
+            native = (grad_params(x, g, weight, bias, s, p, mode, eps, table=ctx.table, cot=cot)
+                      if NATIVE_PARAM_GRADS else None)
+            if native is not None:
+                gw, gb = native
+            else:
+                with torch.enable_grad():
+                    w_ = weight.detach().float().requires_grad_(True)
+                    b_ = bias.detach().float().requires_grad_(True)
+                    out = spectral_forward(x.detach().float(), w_, b_, s, p, mode, eps)
+                    gw, gb = torch.autograd.grad(out, (w_, b_), g.float())
             gw = gw.to(weight.dtype) if ctx.needs_input_grad[1] else None
             gb = gb.to(bias.dtype) if ctx.needs_input_grad[2] else None
         return gx, gw, gb, None, None, None, None, None, None, None

@@ -30,6 +30,9 @@ inline int num_pairs(const FwdParams& P) { return P.C * ((P.B + 1) / 2); }
 
 // Runtime-plan kernel (k_dynamic.cu).
 int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st);
+int launch_xspec(const XspecParams& Q, cudaStream_t st);
+int launch_tap_gradient(const float* g, const float* r, float* out, int nseg, int B, int C, int h, int w, int k,
+                        int s, cudaStream_t st);
 
 // Multi-pass path through a workspace (k_strip.cu).
 int launch_strip(const FwdParams& P, int io_dtype, void* workspace, size_t ws_bytes, cudaStream_t st);

@@ -848,6 +848,111 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
   }
 }
 
+// ---- batch-summed cross spectrum (parameter gradients) ----
+// The operator's multiplier M (G at scale 1, P at scale >= 2) enters the loss only through
+//     L = (1 / (h w)) * Re sum_f M[f] * D[f],   D[f] = sum_b FFT2(pad(x_b))[f] * conj(FFT2(q_b)[f]),
+// q = dL/dout zero-extended (scale 1) or the adjoint of the upsampling epilogue applied to it
+// (scale >= 2), so dL/dweight and dL/dbias follow from D by the chain rule on one (C,h,w) tensor.
+// D is what this kernel computes: a block owns channel c and the batch entries seg, seg + nseg, ...;
+// per entry it loads z = pad(x) + i q into shared memory, runs the forward stages, and with
+// P = Z[f], Q = Z[-f] adds  X conj(Qhat) = ( Im(P Q) / 2,  (|P|^2 - |Q|^2) / 4 )  to its accumulator
+// plane (X = (P + conj Q) / 2 and Qhat = (P - conj Q) / 2i are the spectra of the two real planes).
+// At the end the accumulator is written in natural frequency order: out[seg][c][ky][kx].
+struct XspecParams {
+  const float* x;     // (B,C,H,W)
+  const float* q;     // (B,C,h,w)
+  float2* out;        // [nseg][C][h][w]
+  const float2* tw;   // (cos, sin)(2 pi n / h), n < h, then the same for w
+  int B, C, H, W, p, pad_mode, h, w, pitch, nseg;
+  Plan1D py, px;
+};
+
+CVB_HD size_t xspec_smem_bytes(int h, int w) {
+  const int pitch = w | 1;
+  return (size_t)(2 * h * pitch + h + w) * sizeof(float2) + (size_t)(3 * (h + w)) * sizeof(int);
+}
+
+__host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, int seg, float2* smem, int nthr_emu) {
+  (void)nthr_emu;
+  const int h = Q.h, w = Q.w, pitch = Q.pitch;
+  float2* plane = smem;
+  float2* acc = plane + h * pitch;
+  float2* twy = acc + h * pitch;
+  float2* twx = twy + h;
+  int* fy = (int*)(twx + w);   // position -> frequency
+  int* fx = fy + h;
+  int* ny = fx + w;            // position -> position of the negated frequency
+  int* nx = ny + h;
+  int* oy = nx + w;            // frequency -> position
+  int* ox = oy + h;
+  IoArgs io;
+  io.xa = nullptr; io.xb = nullptr; io.oa = nullptr; io.ob = nullptr;
+  io.H = Q.H; io.W = Q.W; io.p = Q.p; io.pad_mode = Q.pad_mode; io.gelu = 0; io.h = h; io.w = w;
+  io.tab = nullptr; io.rmap = nullptr; io.cmap = nullptr; io.ycopy = nullptr; io.ws = nullptr;
+  io.wes = 0; io.wls = 0; io.xoff = 0; io.yoff = 0;
+  const float invw = 1.0f / (float)w;
+  CVB_PHASE(([&] {
+    for (int i = tid; i < h; i += nthr) {
+      twy[i] = Q.tw[i];
+      const int f = pos_to_freq(Q.py, i);
+      fy[i] = f; oy[f] = i;
+    }
+    for (int i = tid; i < w; i += nthr) {
+      twx[i] = Q.tw[h + i];
+      const int f = pos_to_freq(Q.px, i);
+      fx[i] = f; ox[f] = i;
+    }
+    for (int i = tid; i < h * pitch; i += nthr) acc[i] = make_float2(0.f, 0.f);
+  }()));
+  CVB_PHASE(([&] {
+    for (int i = tid; i < h; i += nthr) ny[i] = oy[(h - fy[i]) % h];
+    for (int i = tid; i < w; i += nthr) nx[i] = ox[(w - fx[i]) % w];
+  }()));
+  const size_t in_plane = (size_t)Q.H * Q.W, q_plane = (size_t)h * w;
+  const int nf = Q.py.nst + Q.px.nst;
+  for (int b = seg; b < Q.B; b += Q.nseg) {
+    const float* xp = Q.x + ((size_t)b * Q.C + c) * in_plane;
+    const float* qp = Q.q + ((size_t)b * Q.C + c) * q_plane;
+    CVB_PHASE(([&] {
+      for (int i = tid; i < h * w; i += nthr) {
+        int row, col;
+        divmod_small(i, w, invw, row, col);
+        const int ry = pad_index(row - Q.p, Q.H, Q.pad_mode);
+        const int cx = pad_index(col - Q.p, Q.W, Q.pad_mode);
+        const float va = (ry >= 0 && cx >= 0) ? xp[(size_t)ry * Q.W + cx] : 0.f;
+        plane[row * pitch + col] = make_float2(va, qp[i]);
+      }
+    }()));
+    for (int ph = 0; ph < nf; ++ph) {
+      const bool along_y = ph < Q.py.nst;
+      const Plan1D& pl = along_y ? Q.py : Q.px;
+      const int i = along_y ? ph : ph - Q.py.nst;
+      CVB_PHASE((run_pass<float>(pl.radix[i], tid, nthr,
+                                 make_pass(plane, along_y, pitch, h, w, pl.n, pl.L[i], pl.M[i],
+                                           along_y ? twy : twx), io, 0)));
+    }
+    CVB_PHASE(([&] {
+      for (int i = tid; i < h * w; i += nthr) {
+        int row, col;
+        divmod_small(i, w, invw, row, col);
+        const float2 P = plane[row * pitch + col];
+        const float2 N = plane[ny[row] * pitch + nx[col]];
+        float2* a = acc + row * pitch + col;
+        a->x += 0.5f * fmaf(P.x, N.y, P.y * N.x);
+        a->y += 0.25f * (fmaf(P.x, P.x, P.y * P.y) - fmaf(N.x, N.x, N.y * N.y));
+      }
+    }()));
+  }
+  float2* op = Q.out + ((size_t)seg * Q.C + c) * q_plane;
+  CVB_PHASE(([&] {
+    for (int i = tid; i < h * w; i += nthr) {
+      int row, col;
+      divmod_small(i, w, invw, row, col);
+      op[(size_t)fy[row] * w + fx[col]] = acc[row * pitch + col];
+    }
+  }()));
+}
+
 // Compile-time plan: h = RY0*RY1, w = RX0*RX1, two stages per axis, NT threads; all
 // index arithmetic is folded by the compiler and only the four needed butterflies
 // count against the kernel's register budget.

@@ -160,7 +160,11 @@ inline void rader_both(const Plan1D& py, const Plan1D& px, RaderInfo& ry, RaderI
 }
 
 // ---- multi-pass (strip) path geometry ----
+#ifdef CVB_WS_TARGET_MB   // tuning builds
+constexpr size_t kWorkspaceTarget = (size_t)CVB_WS_TARGET_MB << 20;
+#else
 constexpr size_t kWorkspaceTarget = 48u << 20;  // chunk workspace kept well inside the 126 MB L2
+#endif
 
 struct StripGeo {
   int cw, rh, halo_l, halo_r;

@@ -31,6 +31,70 @@ int launch_t(const FwdParams& P, size_t smem, cudaStream_t st) {
 }
 }  // namespace
 
+// batch-summed cross spectrum of (pad(x), q): one block per (channel, batch segment)
+__global__ void __launch_bounds__(512, 1) smem_xspec_kernel(const XspecParams Q) {
+  extern __shared__ float2 smem[];
+  smem_block_xspec(Q, blockIdx.x, blockIdx.y, smem, 0);
+}
+
+int launch_xspec(const XspecParams& Q, cudaStream_t st) {
+  const size_t smem = xspec_smem_bytes(Q.h, Q.w);
+  CVB_CUDA(cudaFuncSetAttribute(smem_xspec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int by = Q.w * (Q.h / Q.py.radix[0]), bx = Q.h * (Q.w / Q.px.radix[0]);
+  int nthr = ((by > bx ? by : bx) + 31) / 32 * 32;
+  if (nthr < 64) nthr = 64;
+  if (nthr > 512) nthr = 512;
+  smem_xspec_kernel<<<dim3(Q.C, Q.nseg), nthr, smem, st>>>(Q);
+  CVB_CUDA(cudaGetLastError());
+  return CVB_OK;
+}
+
+// Direct tap term of the scale >= 2 parameter gradient:
+//   out[seg][c][a][b] = sum over batch entries n = seg, seg + nseg, ... and cells m of
+//                       g[n,c,(s my - a + cc) mod s h, (s mx - b + cc) mod s w] * r[n,c,my,mx],   cc = k / 2
+// (the derivative of corr(K, zero_insert_s(r)) with respect to K, models/util_converse.py:171-173 collapsed).
+// One block per (channel, segment); per tap a block-wide sum.
+__global__ void __launch_bounds__(256) tap_gradient_kernel(const float* __restrict__ g, const float* __restrict__ r,
+                                                           float* __restrict__ out, int nseg, int B, int C, int h,
+                                                           int w, int k, int s) {
+  __shared__ float red[8];
+  const int c = blockIdx.x, seg = blockIdx.y, tid = threadIdx.x;
+  const int sh = s * h, sw = s * w, cc = k / 2, cells = h * w;
+  const float invw = 1.0f / (float)w;
+  for (int t = 0; t < k * k; ++t) {
+    const int a = t / k, b = t - a * k;
+    float part = 0.f;
+    for (int n = seg; n < B; n += nseg) {
+      const float* gp = g + ((size_t)n * C + c) * sh * sw;
+      const float* rp = r + ((size_t)n * C + c) * cells;
+      for (int i = tid; i < cells; i += 256) {
+        int my, mx;
+        divmod_small(i, w, invw, my, mx);
+        int gy = s * my - a + cc, gx = s * mx - b + cc;
+        gy += gy < 0 ? sh : (gy >= sh ? -sh : 0);
+        gx += gx < 0 ? sw : (gx >= sw ? -sw : 0);
+        part = fmaf(gp[(size_t)gy * sw + gx], rp[i], part);
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((tid & 31) == 0) red[tid >> 5] = part;
+    __syncthreads();
+    if (tid == 0) {
+      float v = 0.f;
+      for (int i = 0; i < 8; ++i) v += red[i];
+      out[((size_t)seg * C + c) * k * k + t] = v;
+    }
+    __syncthreads();
+  }
+}
+
+int launch_tap_gradient(const float* g, const float* r, float* out, int nseg, int B, int C, int h, int w, int k,
+                        int s, cudaStream_t st) {
+  tap_gradient_kernel<<<dim3(C, nseg), 256, 0, st>>>(g, r, out, nseg, B, C, h, w, k, s);
+  CVB_CUDA(cudaGetLastError());
+  return CVB_OK;
+}
+
 int launch_dynamic(const FwdParams& P, int io_dtype, size_t smem, cudaStream_t st) {
   return io_dtype == CVB_F32 ? launch_t<float>(P, smem, st) : launch_t<__nv_bfloat16>(P, smem, st);
 }

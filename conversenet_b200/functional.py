@@ -79,6 +79,67 @@ def converse2d_forward(x, table, weight_f32, kernel_size, scale, padding, paddin
     return out
 
 
+def cross_spectrum_supported(h, w):
+    """True when `cross_spectrum` has a kernel for the padded plane h x w."""
+    return _cabi.load().cvb_cross_spectrum_supported(int(h), int(w)) == 1
+
+
+def cross_spectrum(x, q, table, padding, padding_mode):
+    """sum_b FFT2(pad(x[b]))  * conj(FFT2(q[b])) per channel, complex64 (C,h,w), natural frequency order.
+
+    x (B,C,H,W), q (B,C,h,w) with h = H + 2*padding: the batch reduction behind dL/dweight and
+    dL/dbias (the reference leaves it to autograd through `torch.fft`, `converse2d.cpp:223`).
+    `table`: a transfer table of the same (C,h,w) (its twiddle tables are used)."""
+    lib = _cabi.load()
+    if not (x.is_cuda and q.is_cuda):
+        raise RuntimeError("cross_spectrum needs CUDA tensors; this build has no CPU path")
+    if padding_mode not in _cabi.PAD_MODES:
+        raise RuntimeError("unknown padding_mode %r" % (padding_mode,))
+    x = x.detach().to(torch.float32).contiguous()
+    q = q.detach().to(torch.float32)
+    B, C, H, W = x.shape
+    p = int(padding)
+    h, w = H + 2 * p, W + 2 * p
+    if tuple(q.shape) != (B, C, h, w):
+        raise RuntimeError("q must be (B,C,H+2p,W+2p)")
+    # The kernel transforms z = pad(x) + i q as one complex plane and separates the two spectra
+    # afterwards; a q far smaller than x (a gradient of a mean loss) would drown in the rounding of
+    # |Z|^2, so each channel of q is brought to the magnitude of x first and the result scaled back.
+    xn = x.square().sum(dim=(0, 2, 3)).sqrt()
+    qn = q.square().sum(dim=(0, 2, 3)).sqrt()
+    gain = torch.where((qn > 0) & (xn > 0), xn / qn.clamp_min(1e-38), torch.ones_like(qn))
+    q = (q * gain.view(1, C, 1, 1)).contiguous()
+    props = torch.cuda.get_device_properties(x.device)
+    nseg = max(1, min(B, (2 * props.multi_processor_count + C - 1) // C))
+    out = torch.empty((nseg, C, h, w, 2), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.cvb_cross_spectrum(x.data_ptr(), q.data_ptr(), table.data_ptr(), out.data_ptr(), nseg, B, C, H, W,
+                                    p, _cabi.PAD_MODES[padding_mode], _stream_ptr(x.device))
+    _cabi.check(rc, "cvb_cross_spectrum")
+    d = torch.view_as_complex(out.sum(0) if nseg > 1 else out[0])
+    return d / gain.view(C, 1, 1)
+
+
+def tap_gradient(g_full, r, kernel_size, scale):
+    """sum_{n,m} g_full[n,c,(s m - a + k//2) mod] r[n,c,m] -> (C,k,k): the direct dependence of the scale >= 2
+    epilogue on the taps (`cvb_tap_gradient`)."""
+    lib = _cabi.load()
+    g_full = g_full.detach().to(torch.float32).contiguous()
+    r = r.detach().to(torch.float32).contiguous()
+    B, C, h, w = r.shape
+    k, s = int(kernel_size), int(scale)
+    if tuple(g_full.shape) != (B, C, s * h, s * w):
+        raise RuntimeError("g_full must be (B,C,s*h,s*w) for r (B,C,h,w)")
+    props = torch.cuda.get_device_properties(r.device)
+    nseg = max(1, min(B, (4 * props.multi_processor_count + C - 1) // C))
+    out = torch.empty((nseg, C, k, k), dtype=torch.float32, device=r.device)
+    with torch.cuda.device(r.device):
+        rc = lib.cvb_tap_gradient(g_full.data_ptr(), r.data_ptr(), out.data_ptr(), nseg, B, C, h, w, k, s,
+                                  _stream_ptr(r.device))
+    _cabi.check(rc, "cvb_tap_gradient")
+    return out.sum(0) if nseg > 1 else out[0]
+
+
 def _f32(t):
     return t.detach().to(torch.float32).contiguous()
 

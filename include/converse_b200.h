@@ -196,6 +196,37 @@ int cvb_converse2d_fwd_static_scratch(const void* x, void* out, const void* tabl
                                       int io_dtype, int fuse_gelu, void* stream);
 
 /*
+ * Batch-summed cross spectrum for the parameter gradients.  The reference obtains dL/dweight and
+ * dL/dbias from autograd through torch.fft (CompositeImplicitAutograd registration,
+ * Converse2D/torch_converse2d/csrc/converse2d.cpp:223); here the batch reduction they need runs in
+ * one kernel:
+ *     out[seg][c][ky][kx] = sum over b = seg, seg + nseg, ... < B of
+ *                           FFT2(pad(x[b,c]))[ky][kx] * conj(FFT2(q[b,c])[ky][kx])
+ * x (B,C,H,W) and q (B,C,h,w) fp32, h = H + 2p, w = W + 2p, unnormalised forward transforms,
+ * frequencies in natural order; out = nseg * C * h * w complex (float2) values, summed over seg
+ * by the caller.  With q = dL/dout zero-extended to the padded plane (scale 1), or the adjoint of
+ * the upsampling epilogue applied to it (scale >= 2), the loss depends on the operator's
+ * multiplier M only through (1 / (h w)) Re sum M * out.  `table`: a transfer table built for
+ * (C, h, w) (its twiddle tables are read).  1 <= nseg <= B.  cvb_cross_spectrum_supported: 1 when
+ * the padded plane fits the kernel (two planes in shared memory, radices with a butterfly), else 0.
+ */
+int cvb_cross_spectrum(const float* x, const float* q, const void* table, void* out, int nseg, int B, int C,
+                       int H, int W, int p, int pad_mode, void* stream);
+int cvb_cross_spectrum_supported(int h, int w);
+
+/*
+ * Direct tap term of dL/dweight at scale >= 2 (the reference: autograd through the correlation of
+ * models/util_converse.py:171-173):
+ *     out[seg][c][a][b] = sum over n = seg, seg + nseg, ... < B and cells (my, mx) of
+ *         g_full[n,c,(s my - a + k/2) mod s h, (s mx - b + k/2) mod s w] * r[n,c,my,mx]
+ * g_full (B,C,s h,s w) = dL/dout zero-extended to the padded grid, r (B,C,h,w) = IFFT2(P . FFT2(pad(x)))
+ * (the forward at scale 1 on the padded planes), all fp32; out = nseg * C * k * k floats, summed over
+ * seg by the caller.
+ */
+int cvb_tap_gradient(const float* g_full, const float* r, float* out, int nseg, int B, int C, int h, int w, int k,
+                     int s, void* stream);
+
+/*
  * Describe the FFT plan chosen for a padded length n: writes up to max_stages
  * radices, returns the stage count, 0 if n is unsupported.  Host-only, no GPU.
  */

@@ -3,7 +3,8 @@
 `tests/golden/converse2d_ref_grads.npz` (written by tests/golden/make_golden.py from the imported
 reference, fp64, loss = y^2 mean: the protocol of the reference's `test/test_error.py:50-54`, plus its
 gradcheck case `:140-153`) holds dL/dx, dL/dweight and dL/dbias.  CPU: the torch.fft restatement that
-supplies parameter gradients is pinned to them; GPU: the module's gradients (native dL/dx) are."""
+is the fallback for parameter gradients is pinned to them; GPU: the module's gradients (native dL/dx,
+parameter gradients from the native batch-summed cross spectrum) are."""
 import ast
 import os
 
@@ -147,7 +148,7 @@ def test_grad_input_matches_autograd_of_the_restatement(case):
     rel = lambda a, r: float((a.detach().double() - r).norm() / r.norm())
     assert rel(y, y64) <= 1e-4
     assert rel(gx, rx) <= 1e-4          # native adjoint
-    assert rel(gw, rw) <= 1e-3          # parameter gradients: fp32 torch.fft restatement
+    assert rel(gw, rw) <= 1e-3          # parameter gradients in fp32 (native cross spectrum, or the fallback)
     # dL/dbias carries sigmoid'(bias - 9) ~ 1e-4 and can sit below fp32 resolution of the O(1) loss
     assert float((gb.double() - rb).norm()) <= 1e-3 * float(rb.norm()) + 1e-8
 
@@ -220,3 +221,104 @@ def test_registered_op_partial_gradients_with_independent_x0(scale):
     assert rel(out, ref) <= 1e-4
     assert rel(gx, rx) <= 1e-4
     assert rel(gx0, rx0) <= 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape,p,mode", [
+    ((3, 4, 30, 38), 2, "replicate"),
+    ((16, 64, 64, 64), 2, "circular"),      # the benchmark layer's planes (68 x 68)
+    ((2, 3, 64, 64), 6, "reflect"),         # 76 x 76 = (19*4)^2: a ConverseDnCNN training patch
+    ((5, 2, 100, 90), 0, "circular"),
+])
+def test_cross_spectrum_matches_torch_fft(shape, p, mode):
+    from conversenet_b200 import functional as CF
+    from conversenet_b200.autograd import _pad
+    torch.manual_seed(5)
+    B, C, H, W = shape
+    h, w = H + 2 * p, W + 2 * p
+    assert CF.cross_spectrum_supported(h, w)
+    x = torch.randn(shape, device="cuda")
+    q = torch.randn(B, C, h, w, device="cuda") * 1e-5     # a gradient's magnitude
+    weight = torch.randn(1, C, 3, 3, device="cuda")
+    bias = torch.zeros(1, C, 1, 1, device="cuda")
+    table, _ = CF.build_transfer(weight, bias, 1, 1e-5, h, w)
+    got = CF.cross_spectrum(x, q, table, p, mode)
+    ref = (torch.fft.fft2(_pad(x.double(), p, mode)) * torch.fft.fft2(q.double()).conj()).sum(0)
+    assert got.shape == ref.shape
+    assert float((got.to(torch.complex128) - ref).norm() / ref.norm()) <= 2e-5
+
+
+@pytest.mark.gpu
+def test_cross_spectrum_refuses_planes_it_has_no_kernel_for():
+    from conversenet_b200 import functional as CF
+    assert not CF.cross_spectrum_supported(268, 268)     # multi-pass planes
+    assert not CF.cross_spectrum_supported(136, 136)     # two planes exceed shared memory
+    x = torch.randn(1, 1, 256, 256, device="cuda")
+    q = torch.randn(1, 1, 268, 268, device="cuda")
+    table, _ = CF.build_transfer(torch.randn(1, 1, 3, 3, device="cuda"), torch.zeros(1, 1, 1, 1, device="cuda"),
+                                 1, 1e-5, 268, 268)
+    with pytest.raises(RuntimeError):
+        CF.cross_spectrum(x, q, table, 6, "circular")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [
+    (4, 8, 64, 64, 5, 1, 2, "circular"),
+    (16, 64, 64, 64, 5, 2, 2, "circular"),   # the benchmark layer
+    (3, 4, 64, 64, 7, 1, 6, "circular"),     # ConverseDnCNN's layer on a 64 x 64 patch
+    (2, 3, 30, 44, 3, 2, 1, "replicate"),
+    (3, 2, 24, 40, 2, 2, 2, "replicate"),    # even kernel
+    (2, 2, 40, 24, 5, 3, 2, "reflect"),
+    (2, 2, 33, 45, 3, 1, 0, "circular"),     # odd plane sizes
+])
+def test_native_parameter_gradients_match_the_torch_fft_route(case):
+    """dL/dweight, dL/dbias from the native cross spectrum against autograd through the restatement
+    (fp32 on the GPU, and fp64)."""
+    from conversenet_b200 import autograd as AG
+    B, C, H, W, k, s, p, mode = case
+    torch.manual_seed(9)
+    weight = torch.randn(1, C, k, k, device="cuda") * 0.2
+    bias = torch.randn(1, C, 1, 1, device="cuda") * 0.5
+    x = torch.randn(B, C, H, W, device="cuda")
+    g = torch.randn(B, C, H * s, W * s, device="cuda")
+    native = AG.grad_params(x, g, weight, bias, s, p, mode, 1e-5)
+    assert native is not None
+    w64 = weight.double().requires_grad_(True)
+    b64 = bias.double().requires_grad_(True)
+    out = AG.spectral_forward(x.double(), w64, b64, s, p, mode, 1e-5)
+    rw, rb = torch.autograd.grad(out, (w64, b64), g.double())
+    assert float((native[0].double() - rw).norm() / rw.norm()) <= 1e-5
+    assert float((native[1].double() - rb).norm()) <= 1e-5 * float(rb.norm()) + 1e-10
+    # and the switch really selects the route
+    m_w = weight.clone().requires_grad_(True)
+    m_b = bias.clone().requires_grad_(True)
+    from conversenet_b200 import functional as CF
+    table, wf = CF.build_transfer(m_w, m_b, s, 1e-5, H + 2 * p, W + 2 * p)
+    outs = []
+    for flag in (True, False):
+        AG.NATIVE_PARAM_GRADS = flag
+        try:
+            y = AG.Converse2DFunction.apply(x, m_w, m_b, table, wf, k, s, p, mode, 1e-5)
+            outs.append(torch.autograd.grad(y, (m_w, m_b), g))
+        finally:
+            AG.NATIVE_PARAM_GRADS = True
+    assert float((outs[0][0] - outs[1][0]).norm() / outs[1][0].norm()) <= 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [(3, 4, 20, 26, 5, 2), (2, 2, 17, 12, 2, 2), (5, 3, 12, 10, 7, 3), (1, 2, 9, 9, 3, 4)])
+def test_tap_gradient_matches_the_sliced_products(case):
+    import torch.nn.functional as F
+    from conversenet_b200 import functional as CF
+    B, C, h, w, k, s = case
+    torch.manual_seed(2)
+    g_full = torch.randn(B, C, s * h, s * w, device="cuda")
+    r = torch.randn(B, C, h, w, device="cuda")
+    got = CF.tap_gradient(g_full, r, k, s)
+    c = k // 2
+    gp = F.pad(g_full.double(), (k - 1 - c, c, k - 1 - c, c), mode="circular")
+    ref = torch.empty(C, k, k, dtype=torch.float64, device="cuda")
+    for a in range(k):
+        for b in range(k):
+            ref[:, a, b] = (gp[..., (k - 1 - a)::s, (k - 1 - b)::s][..., :h, :w] * r.double()).sum(dim=(0, 2, 3))
+    assert float((got.double() - ref).norm() / ref.norm()) <= 1e-5

@@ -177,3 +177,32 @@ def test_emu_gelu_matches_the_erf_definition(emu):
     small = np.abs(x) < 1.0
     assert np.abs(out[small] - ref[small]).max() <= 1.2e-7
     assert np.all(out[x > 6] == x[x > 6]) and np.abs(out[x < -6]).max() < 1e-8
+
+
+@pytest.mark.parametrize("shape,p,mode,nseg", [
+    ((3, 2, 30, 38), 2, "replicate", 2),   # 34 x 42
+    ((4, 1, 64, 64), 2, "circular", 1),    # 68 x 68
+    ((2, 2, 20, 26), 0, "circular", 2),    # no padding
+    ((5, 1, 32, 40), 2, "reflect", 3),     # 36 x 44, uneven segments
+])
+def test_emu_cross_spectrum(emu, shape, p, mode, nseg):
+    # D[c] = sum_b FFT2(pad(x)) conj(FFT2(q)) in natural frequency order, the reduction behind dL/dweight
+    rng = np.random.default_rng(31)
+    B, C, H, W = shape
+    h, w = H + 2 * p, W + 2 * p
+    x = rng.standard_normal(shape).astype(np.float32)
+    q = rng.standard_normal((B, C, h, w)).astype(np.float32)
+    tw = np.zeros((h + w, 2), np.float32)
+    for n, base in ((h, 0), (w, h)):
+        a = 2.0 * np.pi * np.arange(n) / n
+        tw[base:base + n, 0] = np.cos(a)
+        tw[base:base + n, 1] = np.sin(a)
+    out = np.full((nseg, C, h, w, 2), np.nan, np.float32)
+    emu.emu_cross_spectrum.restype = ctypes.c_int
+    rc = emu.emu_cross_spectrum(_ptr(x), _ptr(q), _ptr(tw), _ptr(out), nseg, B, C, H, W, p, PAD[mode], 96)
+    assert rc == 0
+    got = (out[..., 0] + 1j * out[..., 1]).sum(0)
+    y = orc.boundary_pad(x.astype(np.float64), p, mode) if p else x.astype(np.float64)
+    ref = (np.fft.fft2(y) * np.conj(np.fft.fft2(q.astype(np.float64)))).sum(0)
+    assert np.isfinite(out).all()
+    assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 2e-5
