@@ -40,7 +40,7 @@ SIGNATURES = {
     "cvb_fits_shared": (_c.c_int, [_c.c_int, _c.c_int]),
     "cvb_cross_spectrum": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 7 + [_c.c_void_p]),
     "cvb_cross_spectrum_supported": (_c.c_int, [_c.c_int, _c.c_int]),
-    "cvb_tap_gradient": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 8 + [_c.c_void_p]),
+    "cvb_tap_gradient": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 7 + [_c.c_void_p]),
 }
 
 _lib = None

@@ -88,9 +88,69 @@ __global__ void __launch_bounds__(256) tap_gradient_kernel(const float* __restri
   }
 }
 
+// The same sums with the k x k taps of a cell kept in registers (compile-time K): a thread owns cells,
+// reads the K x K window of g around (s my + cc, s mx + cc) and r once per cell; block-wide sums at the end.
+template <int K>
+__global__ void __launch_bounds__(256) tap_gradient_window_kernel(const float* __restrict__ g,
+                                                                  const float* __restrict__ r,
+                                                                  float* __restrict__ out, int nseg, int B, int C,
+                                                                  int h, int w, int s) {
+  __shared__ float red[8];
+  const int c = blockIdx.x, seg = blockIdx.y, tid = threadIdx.x;
+  const int sh = s * h, sw = s * w, cc = K / 2, cells = h * w;
+  const float invw = 1.0f / (float)w;
+  float acc[K * K];
+#pragma unroll
+  for (int t = 0; t < K * K; ++t) acc[t] = 0.f;
+  for (int n = seg; n < B; n += nseg) {
+    const float* gp = g + ((size_t)n * C + c) * sh * sw;
+    const float* rp = r + ((size_t)n * C + c) * cells;
+    for (int i = tid; i < cells; i += 256) {
+      int my, mx;
+      divmod_small(i, w, invw, my, mx);
+      const float rv = rp[i];
+      int gx[K];
+#pragma unroll
+      for (int b = 0; b < K; ++b) {
+        int v = s * mx - b + cc;
+        v += v < 0 ? sw : (v >= sw ? -sw : 0);
+        gx[b] = v;
+      }
+#pragma unroll
+      for (int a = 0; a < K; ++a) {
+        int gy = s * my - a + cc;
+        gy += gy < 0 ? sh : (gy >= sh ? -sh : 0);
+        const float* row = gp + (size_t)gy * sw;
+#pragma unroll
+        for (int b = 0; b < K; ++b) acc[a * K + b] = fmaf(row[gx[b]], rv, acc[a * K + b]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < K * K; ++t) {
+    float part = acc[t];
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((tid & 31) == 0) red[tid >> 5] = part;
+    __syncthreads();
+    if (tid == 0) {
+      float v = 0.f;
+      for (int i = 0; i < 8; ++i) v += red[i];
+      out[((size_t)seg * C + c) * K * K + t] = v;
+    }
+    __syncthreads();
+  }
+}
+
 int launch_tap_gradient(const float* g, const float* r, float* out, int nseg, int B, int C, int h, int w, int k,
                         int s, cudaStream_t st) {
-  tap_gradient_kernel<<<dim3(C, nseg), 256, 0, st>>>(g, r, out, nseg, B, C, h, w, k, s);
+  const dim3 grid(C, nseg);
+  switch (k) {
+    case 2: tap_gradient_window_kernel<2><<<grid, 256, 0, st>>>(g, r, out, nseg, B, C, h, w, s); break;
+    case 3: tap_gradient_window_kernel<3><<<grid, 256, 0, st>>>(g, r, out, nseg, B, C, h, w, s); break;
+    case 5: tap_gradient_window_kernel<5><<<grid, 256, 0, st>>>(g, r, out, nseg, B, C, h, w, s); break;
+    case 7: tap_gradient_window_kernel<7><<<grid, 256, 0, st>>>(g, r, out, nseg, B, C, h, w, s); break;
+    default: tap_gradient_kernel<<<grid, 256, 0, st>>>(g, r, out, nseg, B, C, h, w, k, s); break;
+  }
   CVB_CUDA(cudaGetLastError());
   return CVB_OK;
 }
