@@ -719,6 +719,50 @@ def gpu_library_baseline(R, cfg, K=20):
         torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = tf32
 
 
+def train_step_layer(R, cfg, K=20):
+    """Forward + backward (dL/dx, dL/dweight, dL/dbias) of the configuration's layer through the module, ms per
+    step, beside the same step with the operator written entirely in `torch.fft` (cuFFT + ATen, TF32 off) on the
+    same GPU.  The reference trains through the latter.  Rank 0 at N=1; a side figure, not the headline."""
+    import torch
+    from conversenet_b200 import Converse2D
+    from conversenet_b200.autograd import spectral_forward
+    tf32 = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        m = Converse2D(cfg["C"], cfg["C"], cfg["k"], scale=cfg["s"], padding=cfg["p"], padding_mode=cfg["mode"],
+                       eps=cfg["eps"]).to(R.dev)
+        x = torch.from_numpy(seeded_case(cfg)[0]).to(R.dev).requires_grad_(True)
+        g = torch.randn(cfg["B"], cfg["C"], cfg["H"] * cfg["s"], cfg["W"] * cfg["s"], device=R.dev) * 1e-4
+
+        def ours():
+            torch.autograd.grad(m(x), (x, m.weight, m.bias), g)
+
+        def library():
+            y = spectral_forward(x, m.weight, m.bias, cfg["s"], cfg["p"], cfg["mode"], cfg["eps"])
+            torch.autograd.grad(y, (x, m.weight, m.bias), g)
+
+        out = {}
+        for name, fn in (("ms_per_step", ours), ("torch_fft_ms_per_step", library)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(K):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            out[name] = e0.elapsed_time(e1) / K
+        out["what"] = ("forward + dL/dx + dL/dweight + dL/dbias of the headline layer through the module "
+                       "(native kernels; the chain rule on the (C,h,w) multiplier in PyTorch) against the operator "
+                       "written in torch.fft under autograd; both bound by host launches")
+        out["steps"] = K
+        return out
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = tf32
+
+
 def gpu_library_model(R, workload, batch):
     """The restated reference network on CUDA tensors (torch.fft -> cuFFT, ATen, cuDNN 1x1; TF32 off)."""
     import torch
@@ -843,6 +887,10 @@ def run_ours(args):
                     models[name]["gpu_library_baseline"] = gpu_library_model(R, name, batch)
         except Exception as e:
             line["gpu_library_baseline"] = {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+        try:
+            line["train_step"] = train_step_layer(R, CFG)
+        except Exception as e:
+            line["train_step"] = {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
         try:
             v, info = time_cpu_layer(CFG, budget_s=15.0)
             line["cpu_baseline"] = {"value": v, "unit": "Mpix/s", "cores": info["cores"], "kind": info["kind"],

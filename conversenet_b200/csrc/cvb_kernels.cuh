@@ -858,18 +858,29 @@ __host__ __device__ void smem_block_dynamic(const FwdParams& P, int pair, float2
 // P = Z[f], Q = Z[-f] adds  X conj(Qhat) = ( Im(P Q) / 2,  (|P|^2 - |Q|^2) / 4 )  to its accumulator
 // plane (X = (P + conj Q) / 2 and Qhat = (P - conj Q) / 2i are the spectra of the two real planes).
 // At the end the accumulator is written in natural frequency order: out[seg][c][ky][kx].
+// Planes too large for two shared-memory planes (direct != 0) add every product straight into
+// out[0][c][ky][kx] with atomics instead (the caller zero-fills it).
 struct XspecParams {
   const float* x;     // (B,C,H,W)
   const float* q;     // (B,C,h,w)
   float2* out;        // [nseg][C][h][w]
   const float2* tw;   // (cos, sin)(2 pi n / h), n < h, then the same for w
   int B, C, H, W, p, pad_mode, h, w, pitch, nseg;
+  int direct;         // 1: no accumulator plane, atomic adds into out[0]
   Plan1D py, px;
 };
 
-CVB_HD size_t xspec_smem_bytes(int h, int w) {
+CVB_HD size_t xspec_smem_bytes(int h, int w, int direct) {
   const int pitch = w | 1;
-  return (size_t)(2 * h * pitch + h + w) * sizeof(float2) + (size_t)(3 * (h + w)) * sizeof(int);
+  return (size_t)((direct ? 1 : 2) * h * pitch + h + w) * sizeof(float2) + (size_t)(3 * (h + w)) * sizeof(int);
+}
+
+CVB_HD void xspec_add(float* p, float v) {
+#ifdef __CUDA_ARCH__
+  atomicAdd(p, v);
+#else
+  *p += v;
+#endif
 }
 
 __host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, int seg, float2* smem, int nthr_emu) {
@@ -877,7 +888,7 @@ __host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, in
   const int h = Q.h, w = Q.w, pitch = Q.pitch;
   float2* plane = smem;
   float2* acc = plane + h * pitch;
-  float2* twy = acc + h * pitch;
+  float2* twy = acc + (Q.direct ? 0 : h * pitch);
   float2* twx = twy + h;
   int* fy = (int*)(twx + w);   // position -> frequency
   int* fx = fy + h;
@@ -902,7 +913,8 @@ __host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, in
       const int f = pos_to_freq(Q.px, i);
       fx[i] = f; ox[f] = i;
     }
-    for (int i = tid; i < h * pitch; i += nthr) acc[i] = make_float2(0.f, 0.f);
+    if (!Q.direct)
+      for (int i = tid; i < h * pitch; i += nthr) acc[i] = make_float2(0.f, 0.f);
   }()));
   CVB_PHASE(([&] {
     for (int i = tid; i < h; i += nthr) ny[i] = oy[(h - fy[i]) % h];
@@ -910,6 +922,7 @@ __host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, in
   }()));
   const size_t in_plane = (size_t)Q.H * Q.W, q_plane = (size_t)h * w;
   const int nf = Q.py.nst + Q.px.nst;
+  float2* op = Q.out + ((size_t)(Q.direct ? 0 : seg) * Q.C + c) * q_plane;
   for (int b = seg; b < Q.B; b += Q.nseg) {
     const float* xp = Q.x + ((size_t)b * Q.C + c) * in_plane;
     const float* qp = Q.q + ((size_t)b * Q.C + c) * q_plane;
@@ -937,13 +950,21 @@ __host__ __device__ inline void smem_block_xspec(const XspecParams& Q, int c, in
         divmod_small(i, w, invw, row, col);
         const float2 P = plane[row * pitch + col];
         const float2 N = plane[ny[row] * pitch + nx[col]];
-        float2* a = acc + row * pitch + col;
-        a->x += 0.5f * fmaf(P.x, N.y, P.y * N.x);
-        a->y += 0.25f * (fmaf(P.x, P.x, P.y * P.y) - fmaf(N.x, N.x, N.y * N.y));
+        const float dre = 0.5f * fmaf(P.x, N.y, P.y * N.x);
+        const float dim = 0.25f * (fmaf(P.x, P.x, P.y * P.y) - fmaf(N.x, N.x, N.y * N.y));
+        if (Q.direct) {
+          float* o = (float*)(op + (size_t)fy[row] * w + fx[col]);
+          xspec_add(o, dre);
+          xspec_add(o + 1, dim);
+        } else {
+          float2* a = acc + row * pitch + col;
+          a->x += dre;
+          a->y += dim;
+        }
       }
     }()));
   }
-  float2* op = Q.out + ((size_t)seg * Q.C + c) * q_plane;
+  if (Q.direct) return;
   CVB_PHASE(([&] {
     for (int i = tid; i < h * w; i += nthr) {
       int row, col;

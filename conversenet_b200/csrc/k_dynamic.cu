@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(512, 1) smem_xspec_kernel(const XspecParams Q)
 }
 
 int launch_xspec(const XspecParams& Q, cudaStream_t st) {
-  const size_t smem = xspec_smem_bytes(Q.h, Q.w);
+  const size_t smem = xspec_smem_bytes(Q.h, Q.w, Q.direct);
+  if (Q.direct) CVB_CUDA(cudaMemsetAsync(Q.out, 0, (size_t)Q.C * Q.h * Q.w * sizeof(float2), st));
   CVB_CUDA(cudaFuncSetAttribute(smem_xspec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int by = Q.w * (Q.h / Q.py.radix[0]), bx = Q.h * (Q.w / Q.px.radix[0]);
   int nthr = ((by > bx ? by : bx) + 31) / 32 * 32;

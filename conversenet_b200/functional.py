@@ -81,7 +81,7 @@ def converse2d_forward(x, table, weight_f32, kernel_size, scale, padding, paddin
 
 def cross_spectrum_supported(h, w):
     """True when `cross_spectrum` has a kernel for the padded plane h x w."""
-    return _cabi.load().cvb_cross_spectrum_supported(int(h), int(w)) == 1
+    return _cabi.load().cvb_cross_spectrum_supported(int(h), int(w)) in (1, 2)
 
 
 def cross_spectrum(x, q, table, padding, padding_mode):
@@ -111,12 +111,14 @@ def cross_spectrum(x, q, table, padding, padding_mode):
     q = (q * gain.view(1, C, 1, 1)).contiguous()
     props = torch.cuda.get_device_properties(x.device)
     nseg = max(1, min(B, (2 * props.multi_processor_count + C - 1) // C))
-    out = torch.empty((nseg, C, h, w, 2), dtype=torch.float32, device=x.device)
+    # large planes (kind 2): the blocks add into one slab, which the library zero-fills
+    slabs = 1 if lib.cvb_cross_spectrum_supported(h, w) == 2 else nseg
+    out = torch.empty((slabs, C, h, w, 2), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         rc = lib.cvb_cross_spectrum(x.data_ptr(), q.data_ptr(), table.data_ptr(), out.data_ptr(), nseg, B, C, H, W,
                                     p, _cabi.PAD_MODES[padding_mode], _stream_ptr(x.device))
     _cabi.check(rc, "cvb_cross_spectrum")
-    d = torch.view_as_complex(out.sum(0) if nseg > 1 else out[0])
+    d = torch.view_as_complex(out.sum(0) if slabs > 1 else out[0])
     return d / gain.view(C, 1, 1)
 
 

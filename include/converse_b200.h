@@ -208,7 +208,9 @@ int cvb_converse2d_fwd_static_scratch(const void* x, void* out, const void* tabl
  * the upsampling epilogue applied to it (scale >= 2), the loss depends on the operator's
  * multiplier M only through (1 / (h w)) Re sum M * out.  `table`: a transfer table built for
  * (C, h, w) (its twiddle tables are read).  1 <= nseg <= B.  cvb_cross_spectrum_supported: 1 when
- * the padded plane fits the kernel (two planes in shared memory, radices with a butterfly), else 0.
+ * two padded planes fit shared memory (radices with a butterfly); 2 when only one does: the nseg
+ * blocks of a channel then add into ONE slab with atomics, out = C * h * w values, zero-filled by
+ * this call (summation order, hence the last bits, vary from run to run); else 0.
  */
 int cvb_cross_spectrum(const float* x, const float* q, const void* table, void* out, int nseg, int B, int C,
                        int H, int W, int p, int pad_mode, void* stream);

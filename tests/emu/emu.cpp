@@ -176,14 +176,15 @@ int emu_converse2d_strip2(const float* x, float* out, const void* table, const f
 
 // batch-summed cross spectrum: every (channel, segment) block in turn; `tw` = twiddles of h then w
 int emu_cross_spectrum(const float* x, const float* q, const void* tw, void* out, int nseg, int B, int C, int H,
-                       int W, int p, int pad_mode, int nthr) {
+                       int W, int p, int pad_mode, int nthr, int direct) {
   XspecParams Q;
   Q.x = x; Q.q = q; Q.out = (float2*)out; Q.tw = (const float2*)tw;
   Q.B = B; Q.C = C; Q.H = H; Q.W = W; Q.p = p; Q.pad_mode = pad_mode;
   Q.h = H + 2 * p; Q.w = W + 2 * p; Q.pitch = Q.w | 1; Q.nseg = nseg;
   if (!make_plan(Q.h, Q.py) || !make_plan(Q.w, Q.px)) return -3;
   if (plan_has_big(Q.py) || plan_has_big(Q.px)) return -4;
-  std::vector<float2> smem(xspec_smem_bytes(Q.h, Q.w) / sizeof(float2) + 16);
+  Q.direct = direct;
+  std::vector<float2> smem(xspec_smem_bytes(Q.h, Q.w, direct) / sizeof(float2) + 16);
   for (int c = 0; c < C; ++c)
     for (int seg = 0; seg < nseg; ++seg) smem_block_xspec(Q, c, seg, smem.data(), nthr);
   return 0;

@@ -229,6 +229,8 @@ def test_registered_op_partial_gradients_with_independent_x0(scale):
     ((16, 64, 64, 64), 2, "circular"),      # the benchmark layer's planes (68 x 68)
     ((2, 3, 64, 64), 6, "reflect"),         # 76 x 76 = (19*4)^2: a ConverseDnCNN training patch
     ((5, 2, 100, 90), 0, "circular"),
+    ((6, 3, 128, 128), 4, "replicate"),     # 136 x 136: one plane in shared memory, sums by atomics
+    ((3, 2, 128, 128), 2, "circular"),      # 132 x 132
 ])
 def test_cross_spectrum_matches_torch_fft(shape, p, mode):
     from conversenet_b200 import functional as CF
@@ -252,7 +254,7 @@ def test_cross_spectrum_matches_torch_fft(shape, p, mode):
 def test_cross_spectrum_refuses_planes_it_has_no_kernel_for():
     from conversenet_b200 import functional as CF
     assert not CF.cross_spectrum_supported(268, 268)     # multi-pass planes
-    assert not CF.cross_spectrum_supported(136, 136)     # two planes exceed shared memory
+    assert not CF.cross_spectrum_supported(264, 264)     # one plane exceeds shared memory
     x = torch.randn(1, 1, 256, 256, device="cuda")
     q = torch.randn(1, 1, 268, 268, device="cuda")
     table, _ = CF.build_transfer(torch.randn(1, 1, 3, 3, device="cuda"), torch.zeros(1, 1, 1, 1, device="cuda"),
@@ -270,6 +272,8 @@ def test_cross_spectrum_refuses_planes_it_has_no_kernel_for():
     (3, 2, 24, 40, 2, 2, 2, "replicate"),    # even kernel
     (2, 2, 40, 24, 5, 3, 2, "reflect"),
     (2, 2, 33, 45, 3, 1, 0, "circular"),     # odd plane sizes
+    (4, 2, 128, 128, 5, 1, 4, "replicate"),  # 136 x 136 (ConverseMSRResNet body on 128 x 128 patches)
+    (2, 2, 64, 64, 5, 2, 2, "replicate"),
 ])
 def test_native_parameter_gradients_match_the_torch_fft_route(case):
     """dL/dweight, dL/dbias from the native cross spectrum against autograd through the restatement

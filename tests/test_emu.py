@@ -179,13 +179,14 @@ def test_emu_gelu_matches_the_erf_definition(emu):
     assert np.all(out[x > 6] == x[x > 6]) and np.abs(out[x < -6]).max() < 1e-8
 
 
-@pytest.mark.parametrize("shape,p,mode,nseg", [
-    ((3, 2, 30, 38), 2, "replicate", 2),   # 34 x 42
-    ((4, 1, 64, 64), 2, "circular", 1),    # 68 x 68
-    ((2, 2, 20, 26), 0, "circular", 2),    # no padding
-    ((5, 1, 32, 40), 2, "reflect", 3),     # 36 x 44, uneven segments
+@pytest.mark.parametrize("shape,p,mode,nseg,direct", [
+    ((3, 2, 30, 38), 2, "replicate", 2, 0),   # 34 x 42
+    ((4, 1, 64, 64), 2, "circular", 1, 0),    # 68 x 68
+    ((2, 2, 20, 26), 0, "circular", 2, 0),    # no padding
+    ((5, 1, 32, 40), 2, "reflect", 3, 0),     # 36 x 44, uneven segments
+    ((5, 2, 32, 40), 2, "reflect", 3, 1),     # the large-plane form: sums straight into one slab
 ])
-def test_emu_cross_spectrum(emu, shape, p, mode, nseg):
+def test_emu_cross_spectrum(emu, shape, p, mode, nseg, direct):
     # D[c] = sum_b FFT2(pad(x)) conj(FFT2(q)) in natural frequency order, the reduction behind dL/dweight
     rng = np.random.default_rng(31)
     B, C, H, W = shape
@@ -197,9 +198,9 @@ def test_emu_cross_spectrum(emu, shape, p, mode, nseg):
         a = 2.0 * np.pi * np.arange(n) / n
         tw[base:base + n, 0] = np.cos(a)
         tw[base:base + n, 1] = np.sin(a)
-    out = np.full((nseg, C, h, w, 2), np.nan, np.float32)
+    out = np.zeros((1, C, h, w, 2), np.float32) if direct else np.full((nseg, C, h, w, 2), np.nan, np.float32)
     emu.emu_cross_spectrum.restype = ctypes.c_int
-    rc = emu.emu_cross_spectrum(_ptr(x), _ptr(q), _ptr(tw), _ptr(out), nseg, B, C, H, W, p, PAD[mode], 96)
+    rc = emu.emu_cross_spectrum(_ptr(x), _ptr(q), _ptr(tw), _ptr(out), nseg, B, C, H, W, p, PAD[mode], 96, direct)
     assert rc == 0
     got = (out[..., 0] + 1j * out[..., 1]).sum(0)
     y = orc.boundary_pad(x.astype(np.float64), p, mode) if p else x.astype(np.float64)
