@@ -22,16 +22,20 @@
 // i.e. two real GEMMs D0 = Xr B^T, D1 = Xi B^T (M = 128 vectors, N = NB columns: 2k = C[k],
 // 2k + 1 = S[k]; K = q in chunks of 8), fp32 operands split into TF32 hi + lo, three MMAs per
 // product (hi hi + hi lo + lo hi: fp32 accuracy).  A block has 256 staging / read-back threads (two
-// per vector) and one warp that issues the MMAs: the staging threads request all values of a tile
-// at once (a proxy fence waits for loads in flight, so nothing can be gathered across a staged
-// chunk), split them and write the K-major operand ring (four 16 KB slots), signalling each chunk on
-// a named barrier; the issuing warp issues the chunk's six MMAs and commits to the slot's mbarrier,
-// which is what staging waits for before it reuses the slot.  After the last chunk every thread
-// reads its TMEM lane 16 columns at a time, finishes the stage in registers (lane butterflies are
-// branch-free warp shuffles) and stores.  Blocks are persistent over tiles; the constant operand
-// (hi, lo) arrives once per block by a bulk copy (TMA).  Every mbarrier wait is bounded: after a
-// time-out a thread stops waiting and working but keeps arriving on the barriers, the block sets
-// the status word, frees its TMEM and returns.
+// per vector) and one warp that issues the MMAs.  Modes A, B1, B2: a staging thread writes its four K
+// values of a chunk (hi and lo of both parts) into a ring of 32-column slots in tensor memory behind
+// the accumulators (tcgen05.st), the MMAs read that operand from TMEM -- no shared-memory ring and no
+// generic-to-async proxy fence on the way; the shared memory this frees holds the first chunks of the
+// block's NEXT tile, which each thread requests with cp.async before it reads the current tile back,
+// the remaining chunks are requested when the tile starts and land while the first ones are staged.
+// Mode C (its staging threads produce rows of all four TMEM quadrants) stages K-major operand slots
+// in shared memory.  Either way a chunk is signalled on a named barrier, the issuing warp issues its
+// six MMAs and commits to the slot's mbarrier, which is what staging waits for before it reuses the
+// slot.  After the last chunk every thread reads its TMEM lane 16 columns at a time, finishes the
+// stage in registers (lane butterflies are branch-free warp shuffles) and stores.  Blocks are
+// persistent over tiles; the constant operand (hi, lo) arrives once per block by a bulk copy (TMA).
+// Every mbarrier wait is bounded: after a time-out a thread stops waiting and working but keeps
+// arriving on the barriers, the block sets the status word, frees its TMEM and returns.
 #pragma once
 #include "cvb_strip.cuh"
 #ifdef __CUDACC__
@@ -68,12 +72,34 @@ struct Geo {
 
 CVB_HD constexpr int slots_for(int) { return 4; }   // ring slots: two blocks of R0 <= 96 still share an SM
 
+// Modes A, B1, B2 stage the split operand A in tensor memory (tcgen05.st, read by the MMA from TMEM): no
+// generic-to-async proxy fence on their staging path and no shared-memory ring.  Mode C, whose staging
+// threads write rows of all four TMEM quadrants, keeps the shared-memory ring.
+CVB_HD constexpr bool tmem_a_for(int mode) { return mode != 3; }
+// ring slots of 32 columns (xr hi, xr lo, xi hi, xi lo: 8 each) behind the two accumulators
+template <int R0> CVB_HD constexpr int tmem_a_slots() {
+  return (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 < 4 ? (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 : 4;
+}
+
+// TMEM-staged modes use the ring's shared memory to fetch the first chunks of a block's NEXT tile ahead
+// (cp.async, 8 KB per chunk: 128 rows x 8 K x float2) while the current tile is read back: as many chunks
+// as fit beside the constant operand with the block count per SM unchanged.
+template <int R0> CVB_HD constexpr int prefetch_chunks() {
+  typedef Geo<R0> G;
+  const long long blocks = 512 / G::TMEM_COLS;                                   // per SM, by tensor memory
+  const long long room = 232448 / blocks - 1024 - (long long)(2 * G::B_FLOATS) * 4 - (long long)G::N * 12 - 512;
+  const long long n = room / 8192;
+  return (int)(n < 0 ? 0 : n > G::NCH ? G::NCH : n);
+}
+template <int R0> CVB_HD constexpr size_t ring_bytes(int mode) {
+  return tmem_a_for(mode) ? (size_t)prefetch_chunks<R0>() * 8192 : (size_t)slots_for(mode) * Geo<R0>::SLOT_FLOATS * 4;
+}
+
 // dynamic shared memory of one block
 template <int R0>
 CVB_HD constexpr size_t smem_bytes(int mode) {
   typedef Geo<R0> G;
-  return (size_t)(2 * G::B_FLOATS + slots_for(mode) * G::SLOT_FLOATS) * 4 + (size_t)G::N * 8 + (size_t)G::N * 4 +
-         8 * 8 + 64 + 128;
+  return (size_t)(2 * G::B_FLOATS) * 4 + ring_bytes<R0>(mode) + (size_t)G::N * 8 + (size_t)G::N * 4 + 8 * 8 + 64 + 128;
 }
 
 // float index of element (row, k) of the constant operand (K-major core matrices, no swizzle)
@@ -184,21 +210,21 @@ __device__ __forceinline__ float2 bfly4_spread(float2 a, const Lane4& c) { retur
 __device__ __forceinline__ float2 bfly4_gather(float2 a, const Lane4& c) { return bfly4_lanes<1, 2>(a, c); }
 __device__ __forceinline__ int bitrev2(int j) { return ((j & 1) << 1) | (j >> 1); }
 
-// one thread's 16-byte unit of the four operand arrays (row m, K half `half` of the slot)
-template <int R0>
-__device__ __forceinline__ void stage_quad(float* slot, int m, int half, const float (&re)[4], const float (&im)[4]) {
-  typedef Geo<R0> G;
+// one thread's unit of a K-chunk (row = its TMEM lane, four K values) staged in tensor memory: columns
+// [0,8) xr hi, [8,16) xr lo, [16,24) xi hi, [24,32) xi lo of the slot; `taddr` = this thread's lane, the
+// slot's first column + 4 * K half
+__device__ __forceinline__ void stage_quad_ta(uint32_t taddr, const float (&re)[4], const float (&im)[4]) {
   float rh[4], rl[4], ih[4], il[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     tc::split_tf32(re[e], rh[e], rl[e]);
     tc::split_tf32(im[e], ih[e], il[e]);
   }
-  float* p = slot + (m >> 3) * 32 + (m & 7) * 4 + half * (G::A_LBO / 4);
-  *(float4*)(p + 0 * G::A_FLOATS) = make_float4(rh[0], rh[1], rh[2], rh[3]);
-  *(float4*)(p + 1 * G::A_FLOATS) = make_float4(rl[0], rl[1], rl[2], rl[3]);
-  *(float4*)(p + 2 * G::A_FLOATS) = make_float4(ih[0], ih[1], ih[2], ih[3]);
-  *(float4*)(p + 3 * G::A_FLOATS) = make_float4(il[0], il[1], il[2], il[3]);
+  tc::tmem_st4(taddr + 0, rh[0], rh[1], rh[2], rh[3]);
+  tc::tmem_st4(taddr + 8, rl[0], rl[1], rl[2], rl[3]);
+  tc::tmem_st4(taddr + 16, ih[0], ih[1], ih[2], ih[3]);
+  tc::tmem_st4(taddr + 24, il[0], il[1], il[2], il[3]);
+  tc::tmem_wait_st();
 }
 
 // two consecutive K values (koff, koff + 1; koff even) of row m in the four operand arrays
@@ -234,6 +260,24 @@ __device__ __forceinline__ void issue_chunk(uint32_t tmem, const float* slot, co
     tc::mma_tf32(d, ah, bh, idesc, ch > 0 ? 1u : 0u);
     tc::mma_tf32(d, ah, bl, idesc, 1u);
     tc::mma_tf32(d, al, bh, idesc, 1u);
+  }
+}
+
+// the same with the A operand in tensor memory (slot = 32 columns at `a_tmem`)
+template <int R0>
+__device__ __forceinline__ void issue_chunk_ta(uint32_t tmem, uint32_t a_tmem, const float* b_hi, const float* b_lo,
+                                               int ch) {
+  typedef Geo<R0> G;
+  constexpr uint32_t idesc = tc::idesc_tf32(kVec, G::NB, false, false);
+  const uint64_t bh = tc::smem_desc((const char*)b_hi + ch * G::B_KSTEP, G::B_LBO, 128);
+  const uint64_t bl = tc::smem_desc((const char*)b_lo + ch * G::B_KSTEP, G::B_LBO, 128);
+#pragma unroll
+  for (int part = 0; part < 2; ++part) {
+    const uint32_t ah = a_tmem + (uint32_t)(16 * part), al = ah + 8u;
+    const uint32_t d = tmem + (uint32_t)(part * G::NB);
+    tc::mma_tf32_ta(d, ah, bh, idesc, ch > 0 ? 1u : 0u);
+    tc::mma_tf32_ta(d, ah, bl, idesc, 1u);
+    tc::mma_tf32_ta(d, al, bh, idesc, 1u);
   }
 }
 
@@ -307,6 +351,16 @@ __device__ __forceinline__ void gather_c(const Ident<IO>& id, int sc, int oct, i
   }
 }
 
+// asynchronous copies global -> shared of 8 or 4 bytes; `ok` false writes zeros without reading
+__device__ __forceinline__ void cp_async8(void* dst, const void* src, bool ok) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 8 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, bool ok) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // Named barriers between the 256 staging threads (arrive, never wait) and the issuing warp (sync).  The
 // barrier number is an immediate: with a register operand the compiler reserves all sixteen barriers
 // of the SM for one block.
@@ -351,9 +405,13 @@ __device__ __forceinline__ void bar_sync(int id) {
 template <int R0, int MODE, typename IO>
 __device__ void body(const Params& P, unsigned char* smem_raw) {
   typedef Geo<R0> G;
-  constexpr int NS = slots_for(MODE);
+  constexpr bool TA = tmem_a_for(MODE);
+  constexpr int NS = TA ? tmem_a_slots<R0>() : slots_for(MODE);
+  static_assert(NS >= 2, "operand ring needs two slots");
+  constexpr uint32_t A_BASE = 2 * G::NB;     // first TMEM column of the operand ring (TA)
+  // chunks of the next tile fetched ahead (fp32 tensors: 2-byte elements cannot be copied asynchronously one by one)
+  constexpr int PF = (TA && !(MODE == MODE_A && sizeof(IO) == 2)) ? prefetch_chunks<R0>() : 0;
   constexpr int N = G::N;
-  constexpr int BS = 9;                      // K-chunks gathered at once (modes A, B1, B2)
   constexpr int BSC = 3;                     // mode C: steps gathered at once
   constexpr int NSC = (G::NCH + 1) / 2;      // mode C: steps of two chunks
   constexpr int BAR_FREE = NS + 1;           // named barrier "accumulators read"; slots use 1 .. NS
@@ -370,7 +428,7 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
   float* b_hi = (float*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   float* b_lo = b_hi + G::B_FLOATS;
   float* ring = b_lo + G::B_FLOATS;
-  float2* tw = (float2*)(ring + NS * G::SLOT_FLOATS);
+  float2* tw = (float2*)((char*)ring + ring_bytes<R0>(MODE));
   int* rmap = (int*)(tw + N);
   uint64_t* mbar = (uint64_t*)(((uintptr_t)(rmap + N) + 7) & ~(uintptr_t)7);   // [NS] slots, [NS] = operand B
   uint32_t* holder = (uint32_t*)(mbar + NS + 1);
@@ -411,7 +469,10 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
         tc::fence_after_sync();
         if (lane == 0) {
           if (first && ch == 0) ok = mbar_wait_bounded(&mbar[NS], 0, kWait);   // the constant operand has landed
-          if (ok) issue_chunk<R0>(tmem, ring + slot * G::SLOT_FLOATS, b_hi, b_lo, ch);
+          if (ok) {
+            if (TA) issue_chunk_ta<R0>(tmem, tmem + A_BASE + slot * 32u, b_hi, b_lo, ch);
+            else issue_chunk<R0>(tmem, ring + slot * G::SLOT_FLOATS, b_hi, b_lo, ch);
+          }
           tc::mma_commit(&mbar[slot]);
         }
         __syncwarp();
@@ -432,37 +493,78 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
 
     Ident<IO> id = identify<MODE, IO>(P, blockIdx.x, l, other, nlines);
 
+    // TMEM-staged modes: request the first PF chunks of a tile into this thread's cells of the raw buffer,
+    // [chunk][e][hf][m] float2 (m fastest: no bank conflicts either way)
+    float2* raw = (float2*)ring;
+    auto prefetch = [&](const Ident<IO>& pid) {
+      const float2* gp = pid.ST + (size_t)j * h + pid.pos;
+      const size_t qs = (size_t)4 * h;
+#pragma unroll 1
+      for (int ch = 0; ch < PF; ++ch) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int q = ch * kChunk + 4 * hf + e;
+          float2* dst = raw + (size_t)((ch * 4 + e) * 2 + hf) * kVec + m;
+          const bool live = q < R0 && pid.valid;
+          if (MODE == MODE_A) {
+            const int ro = live ? rmap[4 * q + j] : -1;
+            const bool in = live && (ro | pid.cx) >= 0;
+            const size_t off = in ? (size_t)(ro + pid.cx) : 0;
+            cp_async4(&dst->x, (const float*)pid.xa + off, in);
+            cp_async4(&dst->y, (const float*)(pid.xb ? pid.xb : pid.xa) + off, in && pid.xb != nullptr);
+          } else {
+            cp_async8(dst, live ? (const void*)(gp + qs * q) : (const void*)P.ws, live);
+          }
+        }
+      }
+      cp_async_commit();
+    };
+    if (PF > 0 && blockIdx.x < ntiles) prefetch(id);
+
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const int ntile = tile + gridDim.x;
       const Ident<IO> nid =
           identify<MODE, IO>(P, ntile < ntiles ? ntile : tile, l, other, ntile < ntiles ? nlines : 0);
 
       // ---- gather ahead, split, stage, signal: one K-chunk (two for mode C) per step ----
-      if (MODE != MODE_C) {
-        // A proxy fence waits for the thread's loads in flight, so nothing can be gathered ahead across
-        // a staged chunk: all values of a batch of chunks are requested at once (one memory latency per
-        // batch), then the batch is staged chunk by chunk.
+      if constexpr (TA) {
+        // Operand staged in tensor memory.  The first PF chunks of this tile were fetched into shared memory
+        // by this thread while it read the previous tile back (cp.async; each thread reads only what it
+        // copied itself, so a wait_group is all the ordering needed); the rest is requested now and lands
+        // while those are staged.
         const float2* gp = id.ST + (size_t)j * h + id.pos;
         const size_t qs = (size_t)4 * h;
+        constexpr int NR = G::NCH - PF;
+        float vr[NR > 0 ? NR : 1][4], vi[NR > 0 ? NR : 1][4];
 #pragma unroll
-        for (int b0 = 0; b0 < G::NCH; b0 += BS) {
-          float vr[BS][4], vi[BS][4];
+        for (int cb = 0; cb < NR; ++cb) gather4<R0, MODE, IO>(id, PF + cb, hf, j, gp, qs, rmap, vr[cb], vi[cb]);
+        if (PF > 0) cp_async_wait_all();
+#pragma unroll 1
+        for (int ch = 0; ch < PF; ++ch) {
+          const float2* rp = raw + (size_t)(ch * 8 + hf) * kVec + m;
+          float re[4], im[4];
 #pragma unroll
-          for (int cb = 0; cb < BS; ++cb)
-            if (b0 + cb < G::NCH) gather4<R0, MODE, IO>(id, b0 + cb, hf, j, gp, qs, rmap, vr[cb], vi[cb]);
-#pragma unroll
-          for (int cb = 0; cb < BS; ++cb) {
-            if (b0 + cb < G::NCH) {
-              const uint32_t slot = seq % NS, use = seq / NS;
-              if (use > 0 && ok) ok = mbar_wait_bounded(&mbar[slot], (use - 1) & 1u, kWait);
-              stage_quad<R0>(ring + slot * G::SLOT_FLOATS, m, hf, vr[cb], vi[cb]);
-              tc::fence_proxy_async();
-              tc::fence_before_sync();
-              bar_arrive(1 + (int)slot);
-              seq += 1;
-            }
+          for (int e = 0; e < 4; ++e) {
+            const float2 v = rp[e * 2 * kVec];
+            re[e] = v.x; im[e] = v.y;
           }
+          const uint32_t slot = seq % NS, use = seq / NS;
+          if (use > 0 && ok) ok = mbar_wait_bounded(&mbar[slot], (use - 1) & 1u, kWait);
+          stage_quad_ta(lane_base + A_BASE + slot * 32u + 4u * (uint32_t)hf, re, im);
+          tc::fence_before_sync();
+          bar_arrive(1 + (int)slot);
+          seq += 1;
         }
+#pragma unroll
+        for (int cb = 0; cb < NR; ++cb) {
+          const uint32_t slot = seq % NS, use = seq / NS;
+          if (use > 0 && ok) ok = mbar_wait_bounded(&mbar[slot], (use - 1) & 1u, kWait);
+          stage_quad_ta(lane_base + A_BASE + slot * 32u + 4u * (uint32_t)hf, vr[cb], vi[cb]);
+          tc::fence_before_sync();
+          bar_arrive(1 + (int)slot);
+          seq += 1;
+        }
+        if (PF > 0 && ntile < ntiles) prefetch(nid);   // the raw buffer is free again: next tile's first chunks
       } else {
         // mode C: thread (l, oct) takes k = 16 sc + 2 oct + e, e < 2: 4-point butterfly over the four
         // pos_y = 4k .. 4k + 3 of line x, twiddle, and owns that K pair of rows 32 j + l for j = 0 .. 3
