@@ -6,8 +6,9 @@
 //   A   x (through the pad maps) --R0-point DFT along y--> twiddle --4-point--> S^T[x][pos_y]
 //   B1  S^T --R0-point DFT along x--> twiddle --4-point--> . transfer table, conjugate
 //           --4-point--> twiddle --> S^T (in place; slot x = 4k + j holds inner index j, frequency k)
-//   B2  S^T --R0-point DFT along k--> S^T[x = 4q + j][pos_y]                      (in place)
-//   C   S^T --4-point over pos_y--> twiddle --R0-point DFT along k--> crop, GELU, store
+//   B2  S^T --R0-point DFT along k--> S^T[x = 4q + j][pos_y] --4-point over pos_y = 4k' .. 4k' + 3-->
+//           twiddle --> S^T (in place: the first step of the inverse column transform)
+//   C   S^T --R0-point DFT along k'--> crop, GELU, store
 //       (scale >= 2: the plane r goes back to S^T and a small epilogue kernel finishes)
 //
 // Index conventions are those of the register FFT (cvb_kernels.cuh): decimation in frequency
@@ -22,16 +23,14 @@
 // i.e. two real GEMMs D0 = Xr B^T, D1 = Xi B^T (M = 128 vectors, N = NB columns: 2k = C[k],
 // 2k + 1 = S[k]; K = q in chunks of 8), fp32 operands split into TF32 hi + lo, three MMAs per
 // product (hi hi + hi lo + lo hi: fp32 accuracy).  A block has 256 staging / read-back threads (two
-// per vector) and one warp that issues the MMAs.  Modes A, B1, B2: a staging thread writes its four K
-// values of a chunk (hi and lo of both parts) into a ring of 32-column slots in tensor memory behind
-// the accumulators (tcgen05.st), the MMAs read that operand from TMEM -- no shared-memory ring and no
-// generic-to-async proxy fence on the way; the shared memory this frees holds the first chunks of the
-// block's NEXT tile, which each thread requests with cp.async before it reads the current tile back,
-// the remaining chunks are requested when the tile starts and land while the first ones are staged.
-// Mode C (its staging threads produce rows of all four TMEM quadrants) stages K-major operand slots
-// in shared memory.  Either way a chunk is signalled on a named barrier, the issuing warp issues its
-// six MMAs and commits to the slot's mbarrier, which is what staging waits for before it reuses the
-// slot.  After the last chunk every thread reads its TMEM lane 16 columns at a time, finishes the
+// per vector) and one warp that issues the MMAs.  A staging thread writes its four K values of a chunk
+// (hi and lo of both parts) into a ring of 32-column slots in tensor memory behind the accumulators
+// (tcgen05.st), the MMAs read that operand from TMEM -- no shared-memory operand ring and no
+// generic-to-async proxy fence on the way; shared memory beside the constant operand holds the first
+// chunks of the block's NEXT tile, which each thread requests with cp.async before it reads the current
+// tile back, the remaining chunks are requested when the tile starts and land while the first ones are
+// staged.  A chunk is signalled on a named barrier, the issuing warp issues its six MMAs and commits
+// to the slot's mbarrier, which is what staging waits for before it reuses the slot.  After the last chunk every thread reads its TMEM lane 16 columns at a time, finishes the
 // stage in registers (lane butterflies are branch-free warp shuffles) and stores.  Blocks are
 // persistent over tiles; the constant operand (hi, lo) arrives once per block by a bulk copy (TMA).
 // Every mbarrier wait is bounded: after a time-out a thread stops waiting and working but keeps
@@ -64,26 +63,17 @@ struct Geo {
   static constexpr int NG = (KH + 1 + 7) / 8;                         // read-back groups of 8 k
   static constexpr int B_LBO = (NB / 8) * 128, B_KSTEP = 2 * B_LBO;   // bytes
   static constexpr int B_FLOATS = NCH * (B_KSTEP / 4);                // one array (hi or lo)
-  static constexpr int A_LBO = (kVec / 8) * 128;                      // bytes between the two K halves
-  static constexpr int A_FLOATS = 2 * A_LBO / 4;                      // one array of one chunk: 1024
-  static constexpr int SLOT_FLOATS = 4 * A_FLOATS;                    // xr hi, xr lo, xi hi, xi lo
   static constexpr int TMEM_COLS = 2 * NB <= 32 ? 32 : 2 * NB <= 64 ? 64 : 2 * NB <= 128 ? 128 : 2 * NB <= 256 ? 256 : 512;
 };
 
-CVB_HD constexpr int slots_for(int) { return 4; }   // ring slots: two blocks of R0 <= 96 still share an SM
-
-// Modes A, B1, B2 stage the split operand A in tensor memory (tcgen05.st, read by the MMA from TMEM): no
-// generic-to-async proxy fence on their staging path and no shared-memory ring.  Mode C, whose staging
-// threads write rows of all four TMEM quadrants, keeps the shared-memory ring.
-CVB_HD constexpr bool tmem_a_for(int mode) { return mode != 3; }
 // ring slots of 32 columns (xr hi, xr lo, xi hi, xi lo: 8 each) behind the two accumulators
 template <int R0> CVB_HD constexpr int tmem_a_slots() {
   return (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 < 4 ? (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 : 4;
 }
 
-// TMEM-staged modes use the ring's shared memory to fetch the first chunks of a block's NEXT tile ahead
+// Shared memory beside the constant operand holds the first chunks of a block's NEXT tile, fetched ahead
 // (cp.async, 8 KB per chunk: 128 rows x 8 K x float2) while the current tile is read back: as many chunks
-// as fit beside the constant operand with the block count per SM unchanged.
+// as fit with the block count per SM unchanged.
 template <int R0> CVB_HD constexpr int prefetch_chunks() {
   typedef Geo<R0> G;
   const long long blocks = 512 / G::TMEM_COLS;                                   // per SM, by tensor memory
@@ -91,9 +81,7 @@ template <int R0> CVB_HD constexpr int prefetch_chunks() {
   const long long n = room / 8192;
   return (int)(n < 0 ? 0 : n > G::NCH ? G::NCH : n);
 }
-template <int R0> CVB_HD constexpr size_t ring_bytes(int mode) {
-  return tmem_a_for(mode) ? (size_t)prefetch_chunks<R0>() * 8192 : (size_t)slots_for(mode) * Geo<R0>::SLOT_FLOATS * 4;
-}
+template <int R0> CVB_HD constexpr size_t ring_bytes(int) { return (size_t)prefetch_chunks<R0>() * 8192; }
 
 // dynamic shared memory of one block
 template <int R0>
@@ -227,43 +215,8 @@ __device__ __forceinline__ void stage_quad_ta(uint32_t taddr, const float (&re)[
   tc::tmem_wait_st();
 }
 
-// two consecutive K values (koff, koff + 1; koff even) of row m in the four operand arrays
-template <int R0>
-__device__ __forceinline__ void stage_pair(float* slot, int m, int koff, const float (&re)[2], const float (&im)[2]) {
-  typedef Geo<R0> G;
-  float rh[2], rl[2], ih[2], il[2];
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    tc::split_tf32(re[e], rh[e], rl[e]);
-    tc::split_tf32(im[e], ih[e], il[e]);
-  }
-  float* p = slot + (m >> 3) * 32 + (m & 7) * 4 + (koff & 3) + (koff >> 2) * (G::A_LBO / 4);
-  *(float2*)(p + 0 * G::A_FLOATS) = make_float2(rh[0], rh[1]);
-  *(float2*)(p + 1 * G::A_FLOATS) = make_float2(rl[0], rl[1]);
-  *(float2*)(p + 2 * G::A_FLOATS) = make_float2(ih[0], ih[1]);
-  *(float2*)(p + 3 * G::A_FLOATS) = make_float2(il[0], il[1]);
-}
-
-// the six MMAs of K-chunk `ch` (operands in `slot`), accumulating unless ch == 0
-template <int R0>
-__device__ __forceinline__ void issue_chunk(uint32_t tmem, const float* slot, const float* b_hi, const float* b_lo,
-                                            int ch) {
-  typedef Geo<R0> G;
-  constexpr uint32_t idesc = tc::idesc_tf32(kVec, G::NB, false, false);
-  const uint64_t bh = tc::smem_desc((const char*)b_hi + ch * G::B_KSTEP, G::B_LBO, 128);
-  const uint64_t bl = tc::smem_desc((const char*)b_lo + ch * G::B_KSTEP, G::B_LBO, 128);
-#pragma unroll
-  for (int part = 0; part < 2; ++part) {
-    const uint64_t ah = tc::smem_desc((const char*)(slot + (2 * part) * G::A_FLOATS), G::A_LBO, 128);
-    const uint64_t al = tc::smem_desc((const char*)(slot + (2 * part + 1) * G::A_FLOATS), G::A_LBO, 128);
-    const uint32_t d = tmem + (uint32_t)(part * G::NB);
-    tc::mma_tf32(d, ah, bh, idesc, ch > 0 ? 1u : 0u);
-    tc::mma_tf32(d, ah, bl, idesc, 1u);
-    tc::mma_tf32(d, al, bh, idesc, 1u);
-  }
-}
-
-// the same with the A operand in tensor memory (slot = 32 columns at `a_tmem`)
+// the six MMAs of K-chunk `ch`, accumulating unless ch == 0; operand A in tensor memory (slot = 32 columns at
+// `a_tmem`), the constant operand in shared memory
 template <int R0>
 __device__ __forceinline__ void issue_chunk_ta(uint32_t tmem, uint32_t a_tmem, const float* b_hi, const float* b_lo,
                                                int ch) {
@@ -311,8 +264,8 @@ __device__ __forceinline__ Ident<IO> identify(const Params& P, int tile, int l, 
   return id;
 }
 
-// modes A, B1, B2: the four values q = 8 ch + 4 hf .. + 3 of vector (line, j).  `gp`: address of the
-// vector's element q = 0 in S^T (modes B1, B2); `qs` = 4 h, the stride between consecutive q.
+// the four values q = 8 ch + 4 hf .. + 3 of vector (line, j).  Modes B1, B2, C: `gp` = address of the
+// vector's element q = 0 in S^T, `qs` = the stride between consecutive q (see vector_base)
 template <int R0, int MODE, typename IO>
 __device__ __forceinline__ void gather4(const Ident<IO>& id, int ch, int hf, int j, const float2* gp, size_t qs,
                                         const int* rmap, float (&gr)[4], float (&gi)[4]) {
@@ -334,23 +287,18 @@ __device__ __forceinline__ void gather4(const Ident<IO>& id, int ch, int hf, int
     }
   }
 }
-// mode C: the four pos_y = 4k .. 4k + 3 of line x for k = 16 sc + 2 oct + e, e < 2
-template <int R0, typename IO>
-__device__ __forceinline__ void gather_c(const Ident<IO>& id, int sc, int oct, int h, float4 (&g)[4]) {
-  const float2* row = id.ST + (size_t)id.pos * h;
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const int k = 16 * sc + 2 * oct + e;
-    g[2 * e] = make_float4(0.f, 0.f, 0.f, 0.f);
-    g[2 * e + 1] = g[2 * e];
-    if (k < R0 && id.valid) {
-      const float4* p4 = (const float4*)(row + 4 * k);
-      g[2 * e] = p4[0];
-      g[2 * e + 1] = p4[1];
-    }
+// Where vector (line `id`, inner index j) starts in S^T[x][pos_y] and how far its elements are apart: B1 and
+// B2 transform along x (element q at x = 4 q + j, line = pos_y), C along pos_y (element k at pos_y = 4 k + j,
+// line = x).
+template <int MODE, typename IO>
+__device__ __forceinline__ const float2* vector_base(const Ident<IO>& id, int j, int h, size_t& qs) {
+  if (MODE == MODE_C) {
+    qs = 4;
+    return id.ST + (size_t)id.pos * h + j;
   }
+  qs = (size_t)4 * h;
+  return id.ST + (size_t)j * h + id.pos;
 }
-
 // asynchronous copies global -> shared of 8 or 4 bytes; `ok` false writes zeros without reading
 __device__ __forceinline__ void cp_async8(void* dst, const void* src, bool ok) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 8 : 0) : "memory");
@@ -393,8 +341,8 @@ __device__ __forceinline__ void bar_sync(int id) {
 
 // Block of 288 threads.  Warps 0-7 (256 threads) gather, stage and read back: thread tid serves operand
 // row / TMEM lane m = tid & 127 (warps w and w + 4 share a TMEM quadrant) and takes half hf = tid >> 7
-// of the work on it: K quad hf of every chunk when staging (modes A, B1, B2; in mode C a thread stages
-// a K pair of four rows), read-back groups hf, hf + 2, ...  Warp 8 issues the MMAs: it waits on the
+// of the work on it: K quad hf of every chunk when staging, read-back groups hf, hf + 2, ...  Warp 8
+// issues the MMAs: it waits on the
 // named barrier of a ring slot for the 256 arrivals of the chunk staged there, issues the chunk's six
 // MMAs and commits them to the slot's mbarrier, which is what a staging thread waits for before it
 // reuses the slot -- so staging never waits for the issue, only for the tensor cores three chunks back.
@@ -405,15 +353,12 @@ __device__ __forceinline__ void bar_sync(int id) {
 template <int R0, int MODE, typename IO>
 __device__ void body(const Params& P, unsigned char* smem_raw) {
   typedef Geo<R0> G;
-  constexpr bool TA = tmem_a_for(MODE);
-  constexpr int NS = TA ? tmem_a_slots<R0>() : slots_for(MODE);
+  constexpr int NS = tmem_a_slots<R0>();
   static_assert(NS >= 2, "operand ring needs two slots");
-  constexpr uint32_t A_BASE = 2 * G::NB;     // first TMEM column of the operand ring (TA)
+  constexpr uint32_t A_BASE = 2 * G::NB;     // first TMEM column of the operand ring
   // chunks of the next tile fetched ahead (fp32 tensors: 2-byte elements cannot be copied asynchronously one by one)
-  constexpr int PF = (TA && !(MODE == MODE_A && sizeof(IO) == 2)) ? prefetch_chunks<R0>() : 0;
+  constexpr int PF = (MODE == MODE_A && sizeof(IO) == 2) ? 0 : prefetch_chunks<R0>();
   constexpr int N = G::N;
-  constexpr int BSC = 3;                     // mode C: steps gathered at once
-  constexpr int NSC = (G::NCH + 1) / 2;      // mode C: steps of two chunks
   constexpr int BAR_FREE = NS + 1;           // named barrier "accumulators read"; slots use 1 .. NS
   const FwdParams& F = P.f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -469,10 +414,7 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
         tc::fence_after_sync();
         if (lane == 0) {
           if (first && ch == 0) ok = mbar_wait_bounded(&mbar[NS], 0, kWait);   // the constant operand has landed
-          if (ok) {
-            if (TA) issue_chunk_ta<R0>(tmem, tmem + A_BASE + slot * 32u, b_hi, b_lo, ch);
-            else issue_chunk<R0>(tmem, ring + slot * G::SLOT_FLOATS, b_hi, b_lo, ch);
-          }
+          if (ok) issue_chunk_ta<R0>(tmem, tmem + A_BASE + slot * 32u, b_hi, b_lo, ch);
           tc::mma_commit(&mbar[slot]);
         }
         __syncwarp();
@@ -485,10 +427,9 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
   } else {
     // ---------------- the 256 staging / read-back threads ----------------
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    // modes A, B1, B2: row m = vector (line l = m / 4, inner index j = m % 4)
-    // mode C: staging thread = (line l = lane, pair of k given by the warp); read-back row m = 32 j + l
-    const int l = (MODE == MODE_C) ? lane : (m >> 2);
-    const int j = (MODE == MODE_C) ? (warp & 3) : (m & 3);
+    // row m = vector (line l = m / 4, inner index j = m % 4)
+    const int l = m >> 2;
+    const int j = m & 3;
     const size_t in_plane = (size_t)F.H * F.W;
 
     Ident<IO> id = identify<MODE, IO>(P, blockIdx.x, l, other, nlines);
@@ -497,8 +438,8 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
     // [chunk][e][hf][m] float2 (m fastest: no bank conflicts either way)
     float2* raw = (float2*)ring;
     auto prefetch = [&](const Ident<IO>& pid) {
-      const float2* gp = pid.ST + (size_t)j * h + pid.pos;
-      const size_t qs = (size_t)4 * h;
+      size_t qs;
+      const float2* gp = vector_base<MODE, IO>(pid, j, h, qs);
 #pragma unroll 1
       for (int ch = 0; ch < PF; ++ch) {
 #pragma unroll
@@ -527,13 +468,13 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
           identify<MODE, IO>(P, ntile < ntiles ? ntile : tile, l, other, ntile < ntiles ? nlines : 0);
 
       // ---- gather ahead, split, stage, signal: one K-chunk (two for mode C) per step ----
-      if constexpr (TA) {
+      {
         // Operand staged in tensor memory.  The first PF chunks of this tile were fetched into shared memory
         // by this thread while it read the previous tile back (cp.async; each thread reads only what it
         // copied itself, so a wait_group is all the ordering needed); the rest is requested now and lands
         // while those are staged.
-        const float2* gp = id.ST + (size_t)j * h + id.pos;
-        const size_t qs = (size_t)4 * h;
+        size_t qs;
+        const float2* gp = vector_base<MODE, IO>(id, j, h, qs);
         constexpr int NR = G::NCH - PF;
         float vr[NR > 0 ? NR : 1][4], vi[NR > 0 ? NR : 1][4];
 #pragma unroll
@@ -565,51 +506,6 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
           seq += 1;
         }
         if (PF > 0 && ntile < ntiles) prefetch(nid);   // the raw buffer is free again: next tile's first chunks
-      } else {
-        // mode C: thread (l, oct) takes k = 16 sc + 2 oct + e, e < 2: 4-point butterfly over the four
-        // pos_y = 4k .. 4k + 3 of line x, twiddle, and owns that K pair of rows 32 j + l for j = 0 .. 3
-#pragma unroll
-        for (int s0 = 0; s0 < NSC; s0 += BSC) {
-          float4 vc[BSC][4];
-#pragma unroll
-          for (int sb = 0; sb < BSC; ++sb)
-            if (s0 + sb < NSC) gather_c<R0, IO>(id, s0 + sb, warp, h, vc[sb]);
-#pragma unroll
-          for (int sb = 0; sb < BSC; ++sb) {
-            const int sc = s0 + sb;
-            if (sc < NSC) {
-              const int ch = 2 * sc + (warp >> 2);            // the chunk this thread contributes to
-              const int nch = (2 * sc + 1 < G::NCH) ? 2 : 1;  // chunks of this step
-              const uint32_t slot0 = seq % NS, use0 = seq / NS, slot1 = (seq + 1) % NS, use1 = (seq + 1) / NS;
-              if (use0 > 0 && ok) ok = mbar_wait_bounded(&mbar[slot0], (use0 - 1) & 1u, kWait);
-              if (nch == 2 && use1 > 0 && ok) ok = mbar_wait_bounded(&mbar[slot1], (use1 - 1) & 1u, kWait);
-              if (ch < G::NCH) {
-                float orr[4][2], oi[4][2];   // [j][e]
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const int k = 16 * sc + 2 * warp + e;
-                  float re[4] = {vc[sb][2 * e].x, vc[sb][2 * e].z, vc[sb][2 * e + 1].x, vc[sb][2 * e + 1].z};
-                  float im[4] = {vc[sb][2 * e].y, vc[sb][2 * e].w, vc[sb][2 * e + 1].y, vc[sb][2 * e + 1].w};
-                  Radix<4>::fwd(re, im);
-#pragma unroll
-                  for (int jj = 0; jj < 4; ++jj) {
-                    float2 v = make_float2(re[jj], im[jj]);
-                    if (jj > 0 && k < R0) v = mul_conj(v, tw[jj * k]);
-                    orr[jj][e] = v.x; oi[jj][e] = v.y;
-                  }
-                }
-                float* sp = ring + ((warp >> 2) ? slot1 : slot0) * G::SLOT_FLOATS;
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) stage_pair<R0>(sp, 32 * jj + lane, 2 * (warp & 3), orr[jj], oi[jj]);
-              }
-              tc::fence_proxy_async();
-              tc::fence_before_sync();
-              bar_arrive(1 + (int)slot0);
-              if (nch == 2) bar_arrive(1 + (int)slot1);
-              seq += nch;
-            }
-          }
-        }
       }
 
       // ---- wait for the tile's last MMAs, read this thread's TMEM lane back, finish the stage ----
@@ -630,6 +526,14 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
         live = k <= G::KH && !(mir && (k == 0 || 2 * k == R0));
         return live ? (mir ? R0 - k : k) : 0;
       };
+      // mode B2 also runs the first step of the inverse column transform: the 4-point DFT over the four
+      // pos_y = 4 k' .. 4 k' + 3 of a column (four consecutive lines = lanes 4 apart; tiles and planes start
+      // at multiples of four lines) and its twiddle, so that kernel C gathers finished vectors.  Lane i4 of
+      // the four ends up with output index bitrev2(i4), stored at pos_y = 4 k' + bitrev2(i4).
+      const int i4 = l & 3, jy = bitrev2(i4), kprime = pos >> 2;
+      const Lane4 lsy = lane4_spread(i4);
+      float2 twy = make_float2(1.f, 0.f);
+      if (MODE == MODE_B2) twy = (F.table + (size_t)F.C * h * w)[jy * kprime];   // y-axis twiddle (cos, sin)(2 pi jy k' / h)
       const float2* tabp = tab + (size_t)jr * h + pos;     // mode B1: element (4 kq + jr, pos) at tabp[4 h kq]
       float2 gn[8];                                        // mode B1: table values of the next half-group
       if (MODE == MODE_B1) {
@@ -676,6 +580,10 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = bfly4_spread(mul_conj(v[i], t1[i]), ls);
           }
+          if (MODE == MODE_B2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = mul_conj(bfly4_lanes<8, 4>(v[i], lsy), twy);
+          }
           if (MODE == MODE_B1) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -689,8 +597,10 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
             if (!(valid && live[i])) continue;
             if (MODE == MODE_A) {
               ST[(size_t)pos * h + 4 * kq[i] + jr] = v[i];
-            } else if (MODE == MODE_B1 || MODE == MODE_B2) {
+            } else if (MODE == MODE_B1) {
               ST[(size_t)(4 * kq[i] + j) * h + pos] = v[i];
+            } else if (MODE == MODE_B2) {
+              ST[(size_t)(4 * kq[i] + j) * h + 4 * kprime + jy] = v[i];
             } else {
               const int y = 4 * kq[i] + j;
               if (F.s > 1) {
