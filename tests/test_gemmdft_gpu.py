@@ -1,4 +1,4 @@
-"""The tensor-core multi-pass kernels (padded lengths 4 * R0 with R0 in the registry: 268 and 512)
+"""The tensor-core multi-pass kernels (padded lengths 4 * R0 with R0 in the registry: 268, 512 and 516)
 against the numpy oracle, through the C ABI: square and non-square planes, an unpaired plane (odd
 batch), every padding mode, bf16 tensors, the fused GELU and the scale >= 2 epilogue kernel."""
 import numpy as np
@@ -15,6 +15,8 @@ CASES = [
     dict(B=2, C=1, H=512, W=512, k=7, s=1, p=0, mode="circular"),      # 512 x 512, the USRNet data step
     dict(B=1, C=2, H=500, W=256, k=3, s=1, p=6, mode="replicate"),     # 512 x 268
     dict(B=2, C=2, H=264, W=264, k=5, s=2, p=2, mode="constant"),      # 268 x 268 at scale 2: epilogue kernel
+    dict(B=2, C=2, H=512, W=512, k=3, s=1, p=2, mode="circular"),      # 516 x 516, the USRNet blocks' layer
+    dict(B=1, C=1, H=512, W=264, k=3, s=1, p=2, mode="replicate"),     # 516 x 268
 ]
 
 

@@ -80,9 +80,14 @@ def test_network_at_benchmark_resolution(fx, case, pset):
     assert out[..., ::st, ::st].shape == sub.shape
     err = orc.rel_l2(out[..., ::st, ::st], sub)
     print("%s: rel L2 vs reference fp64 %.2e (reference fp32 drift %.2e)" % (key, err, drift))
-    assert err <= max(1e-4, drift)
+    # Trained weights: at least as close to fp64 as the reference's own fp32 run (or 1e-4).  Random weights: the
+    # networks amplify fp32 rounding (ConverseUSRNet at scale 1 by ~1e3: the reference's own fp32 run is 2.7e-3 from
+    # its fp64 run), so two fp32 implementations differ from fp64 by noise of the same size, not by the same noise;
+    # the bar there is 1.5 x the reference's drift.
+    bar = max(1e-4, drift if pset == "ckpt" else 1.5 * drift)
+    assert err <= bar
     norm = float(fx[key + "_norm"])
-    assert abs(float(np.linalg.norm(out.astype(np.float64))) - norm) <= max(1e-4, drift) * norm
+    assert abs(float(np.linalg.norm(out.astype(np.float64))) - norm) <= bar * norm
     from conversenet_b200 import _cabi
     assert _cabi.load().cvb_last_device_status(1) == 0
 
