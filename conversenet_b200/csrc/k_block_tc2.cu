@@ -235,11 +235,18 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
       const long long pix0 = tile * kT2Tile;
       const int b = (int)(pix0 / P.HW);
       const int p0 = (int)(pix0 - (long long)b * P.HW);
-      if (!t2_wait(&tfull[acc], (uint32_t)((it >> 1) & 1), abort_flag)) break;
-      tc::fence_after_sync();
       const size_t off = (size_t)b * N * P.HW + p0 + cw * 32 + lane;
       IO* ob = (IO*)P.out + off;
       const IO* rb = (const IO*)P.x + off;   // residual (MODE 1)
+      // MODE 1: the residual values of the first 32 channels are requested before the wait for the
+      // accumulator, those of the next 32 before the first are used, so their latency is off the path
+      float r[MODE == 1 ? 32 : 1];
+      if (MODE == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = ld_io<IO>(rb, (size_t)j * P.HW);
+      }
+      if (!t2_wait(&tfull[acc], (uint32_t)((it >> 1) & 1), abort_flag)) break;
+      tc::fence_after_sync();
 #pragma unroll 1
       for (int c0 = 0; c0 < N; c0 += 32) {
         float a32[32];
@@ -248,12 +255,15 @@ __global__ void __launch_bounds__(kT2Threads, 1) tc_pw_kernel(const BlockParams 
 #pragma unroll
           for (int j = 0; j < 32; ++j) st_io<IO>(ob, (size_t)(c0 + j) * P.HW, gelu_erf(a32[j] + bias[c0 + j]));
         } else {
-          float r[32];
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = ld_io<IO>(rb, (size_t)(c0 + j) * P.HW);
+          for (int j = 0; j < 32; ++j) v[j] = fmaf(alpha[c0 + j], a32[j] + bias[c0 + j], r[j]);
+          if (c0 + 32 < N) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            st_io<IO>(ob, (size_t)(c0 + j) * P.HW, fmaf(alpha[c0 + j], a32[j] + bias[c0 + j], r[j]));
+            for (int j = 0; j < 32; ++j) r[j] = ld_io<IO>(rb, (size_t)(c0 + 32 + j) * P.HW);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st_io<IO>(ob, (size_t)(c0 + j) * P.HW, v[j]);
         }
       }
       tc::fence_before_sync();
