@@ -50,6 +50,8 @@ int launch_pw_res_tc(const BlockParams& P, int sms, int* status, cudaStream_t st
 // warp-specialised, double-buffered versions of the two (k_block_tc2.cu)
 int launch_ln_pw_gelu_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
 int launch_pw_res_tc2(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
+int launch_ln_pw_gelu_tc3(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
+int launch_pw_res_tc3(const BlockParams& P, int io_dtype, int sms, int* status, cudaStream_t st);
 
 // Multi-pass kernels with a compile-time axis plan (k_strip2.cu, one object per registry line).
 struct StripParams;

@@ -169,7 +169,7 @@ def pw_res_mlp(t, x, conv_out, ln, conv_up, conv_down, alpha1=None, alpha2=None)
     x = x.contiguous()
     B, C, H, W = x.shape
     bk = lib.cvb_get_option(_cabi.OPT_BLOCK_KERNELS)
-    if (H * W) % 128 == 0 and (bk == 2 or (bk == 1 and x.dtype == torch.float32)):
+    if (H * W) % 128 == 0 and (bk >= 2 or (bk == 1 and x.dtype == torch.float32)):
         # tensor-core route: three tcgen05 kernels (1x1 + residual, LN + 1x1 + GELU, 1x1 + residual)
         x1 = pw_res(t, x, conv_out, alpha1)
         hid = ln_pw_gelu(x1, ln, conv_up)

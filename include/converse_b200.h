@@ -62,7 +62,8 @@ enum {
   CVB_OPT_MULTIPASS = 1,      /* 1: every plane takes the multi-pass path through the workspace     */
   CVB_OPT_PERSISTENT = 2,     /* 1: compile-time-plan kernels run as persistent blocks with prefetch */
   CVB_OPT_BLOCK_KERNELS = 3,  /* ConverseBlock 1x1 kernels: 0 CUDA cores, 1 tcgen05 single-buffered,
-                                 2 tcgen05 warp-specialised (default)                               */
+                                 2 tcgen05 warp-specialised, operand tiles in shared memory,
+                                 3 tcgen05 warp-specialised, cp.async ring + operand in TMEM (default) */
   CVB_OPT_COUNT_ = 4
 };
 int cvb_set_option(int which, int value);   /* CVB_OK or CVB_ERR_BAD_ARGUMENT */

@@ -128,8 +128,9 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(monkeypatch):
         ref = CF.ln_pw_gelu(x, ln, conv)
     with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 1):    # single-buffered kernel
         out1 = CF.ln_pw_gelu(x, ln, conv)
-    assert _cabi.load().cvb_get_option(_cabi.OPT_BLOCK_KERNELS) == 2   # warp-specialised, double-buffered: default
-    out = CF.ln_pw_gelu(x, ln, conv)
+    assert _cabi.load().cvb_get_option(_cabi.OPT_BLOCK_KERNELS) == 3   # default: operand in tensor memory
+    with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 2):    # warp-specialised, operand tiles in shared memory
+        out = CF.ln_pw_gelu(x, ln, conv)
     torch.cuda.synchronize()
     assert _cabi.load().cvb_last_device_status(1) == 0
     assert float((out1 - ref).norm() / ref.norm()) <= 3e-6
@@ -202,3 +203,40 @@ def test_graphed_forward_replays_the_eager_result():
     assert torch.equal(g(x2).clone(), want2)
     with pytest.raises(RuntimeError):
         g(torch.rand(1, 1, 40, 56, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_kernels_with_the_operand_in_tensor_memory(dtype):
+    """Option value 3 of the block kernels (cp.async ring, LayerNorm inside one thread, operand A staged in TMEM)
+    against fp32 PyTorch and against variant 2, on images of many tiles and on a single tile."""
+    from conversenet_b200 import functional as CF, _cabi
+    from conversenet_b200.util_converse import LayerNorm
+    torch.backends.cudnn.allow_tf32 = False
+    torch.manual_seed(8)
+    ln = LayerNorm(64, eps=1e-5, data_format="channels_first").cuda()
+    conv = torch.nn.Conv2d(64, 128, 1).cuda()
+    conv2 = torch.nn.Conv2d(128, 64, 1).cuda()
+    with torch.no_grad():
+        ln.weight.add_(0.3 * torch.randn_like(ln.weight))
+        ln.bias.add_(0.2 * torch.randn_like(ln.bias))
+    alpha = torch.randn(1, 64, 1, 1, device="cuda")
+    tol = 5e-6 if dtype == torch.float32 else 4e-3
+    for shape in ((3, 64, 96), (1, 8, 16), (5, 128, 128)):
+        B, H, W = shape
+        x = torch.randn(B, 64, H, W, device="cuda").to(dtype)
+        t = torch.randn(B, 128, H, W, device="cuda").to(dtype)
+        with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 3):
+            out = CF.ln_pw_gelu(x, ln, conv)
+            got2 = CF.pw_res(t, x, conv2, alpha)
+        with _cabi.option(_cabi.OPT_BLOCK_KERNELS, 2):
+            ref = CF.ln_pw_gelu(x, ln, conv)
+            ref2 = CF.pw_res(t, x, conv2, alpha)
+        torch.cuda.synchronize()
+        assert _cabi.load().cvb_last_device_status(1) == 0
+        with torch.no_grad():
+            want = torch.nn.functional.gelu(conv(ln(x.float())))
+            want2 = x.float() + alpha * conv2(t.float())
+        assert float((out.float() - want).norm() / want.norm()) <= tol, shape
+        assert float((got2.float() - want2).norm() / want2.norm()) <= tol, shape
+        assert float((out.float() - ref.float()).norm() / ref.float().norm()) <= tol
+        assert float((got2.float() - ref2.float()).norm() / ref2.float().norm()) <= tol
