@@ -159,18 +159,108 @@ class Emitter:
         return out
 
 
+class Emitter2(Emitter):
+    """The same butterflies on PACKED complex values: one 64-bit register pair holds (re, im) and the
+    additions, multiplications by a real constant and fused multiply-adds act on both halves with one
+    instruction (add / mul / fma .f32x2 of sm_100).  Nearly every operation of these codelets treats the
+    real and the imaginary part alike, so the instruction count of a butterfly drops by about 40 %.
+    A value name stands for a `p2` variable."""
+
+    def let(self, expr):
+        name = self.tmp()
+        self.lines.append(f"    const p2 {name} = {expr};")
+        return name
+
+    @staticmethod
+    def both(v):
+        return f"p2_pack({flit(v)}, {flit(v)})"
+
+    def cadd(self, x, y):
+        return self.let(f"p2_add({x}, {y})")
+
+    def csub(self, x, y):
+        return self.let(f"p2_sub({x}, {y})")
+
+    def parts(self, x):
+        r, i = self.tmp(), self.tmp()
+        self.lines.append(f"    float {r}, {i}; p2_unpack({x}, {r}, {i});")
+        return r, i
+
+    def mul_neg_i(self, x):  # (a+ib)(-i) = b - ia
+        r, i = self.parts(x)
+        return self.let(f"p2_pack({i}, -{r})")
+
+    def mul_pos_i(self, x):  # (a+ib) i = -b + ia
+        r, i = self.parts(x)
+        return self.let(f"p2_pack(-{i}, {r})")
+
+    def twiddle(self, x, num, den):
+        """x * exp(-2 pi i num/den)."""
+        num %= den
+        if num == 0:
+            return x
+        if 4 * num == den:
+            return self.mul_neg_i(x)
+        if 2 * num == den:
+            return self.let(f"p2_mul({x}, {self.both(-1.0)})")
+        if 4 * num == 3 * den:
+            return self.mul_pos_i(x)
+        th = 2.0 * math.pi * num / den
+        c, s = math.cos(th), math.sin(th)
+        # (a + ib)(c - is) = (a c + b s, b c - a s) = (a, b) * (c, c) + (b, a) * (s, -s)
+        r, i = self.parts(x)
+        sw = self.let(f"p2_pack({i}, {r})")
+        return self.let(f"p2_fma({sw}, p2_pack({flit(s)}, {flit(-s)}), p2_mul({x}, {self.both(c)}))")
+
+    def dft_odd_prime(self, xs):
+        R = len(xs)
+        hn = (R - 1) // 2
+        s = [None] + [self.cadd(xs[j], xs[R - j]) for j in range(1, hn + 1)]
+        d = [None] + [self.csub(xs[j], xs[R - j]) for j in range(1, hn + 1)]
+        acc = xs[0]
+        for j in range(1, hn + 1):
+            acc = self.cadd(acc, s[j])
+        out = [None] * R
+        out[0] = acc
+        for k in range(1, hn + 1):
+            a = xs[0]
+            b = None
+            for j in range(1, hn + 1):
+                th = 2.0 * math.pi * ((j * k) % R) / R
+                c, sn = math.cos(th), math.sin(th)
+                a = self.let(f"p2_fma({self.both(c)}, {s[j]}, {a})")
+                if b is None:
+                    b = self.let(f"p2_mul({self.both(sn)}, {d[j]})")
+                else:
+                    b = self.let(f"p2_fma({self.both(sn)}, {d[j]}, {b})")
+            # X_k = a - i b = a + (b.im, -b.re),  X_{R-k} = a + i b = a - (b.im, -b.re)
+            w = self.mul_neg_i(b)
+            out[k] = self.cadd(a, w)
+            out[R - k] = self.csub(a, w)
+        return out
+
+
 def gen(R):
     e = Emitter()
     xs = [(f"re[{i}]", f"im[{i}]") for i in range(R)]
     out = e.dft(xs)
+    e2 = Emitter2()
+    out2 = e2.dft([f"z{i}" for i in range(R)])
     lines = [f"template <> struct Radix<{R}> {{",
-             f"  static CVB_HD void fwd(float (&re)[{R}], float (&im)[{R}]) {{"]
+             f"  static CVB_HD void fwd(float (&re)[{R}], float (&im)[{R}]) {{",
+             "#if defined(__CUDA_ARCH__) && !defined(CVB_SCALAR_CODELETS)"]
+    for i in range(R):
+        lines.append(f"    const p2 z{i} = p2_pack(re[{i}], im[{i}]);")
+    lines += e2.lines
+    for i, z in enumerate(out2):
+        lines.append(f"    p2_unpack({z}, re[{i}], im[{i}]);")
+    lines.append("#else")
     lines += e.lines
     for i, (r, m) in enumerate(out):
         lines.append(f"    const float o{i}r = {r}, o{i}i = {m};")
     for i in range(R):
         lines.append(f"    re[{i}] = o{i}r; im[{i}] = o{i}i;")
-    lines += ["  }", "};", ""]
+    lines += ["#endif", "  }", "};", ""]
     return "\n".join(lines)
 
 
@@ -181,6 +271,16 @@ def main():
     print("#define CVB_HD __host__ __device__ __forceinline__")
     print("#endif")
     print("namespace cvb {")
+    print("#ifdef __CUDA_ARCH__")
+    print("// packed (re, im) pairs and the two-wide fp32 instructions of sm_100")
+    print("typedef unsigned long long p2;")
+    print("__device__ __forceinline__ p2 p2_pack(float x, float y) { p2 r; asm(\"mov.b64 %0, {%1, %2};\" : \"=l\"(r) : \"f\"(x), \"f\"(y)); return r; }")
+    print("__device__ __forceinline__ void p2_unpack(p2 v, float& x, float& y) { asm(\"mov.b64 {%0, %1}, %2;\" : \"=f\"(x), \"=f\"(y) : \"l\"(v)); }")
+    print("__device__ __forceinline__ p2 p2_add(p2 a, p2 b) { p2 r; asm(\"add.rn.f32x2 %0, %1, %2;\" : \"=l\"(r) : \"l\"(a), \"l\"(b)); return r; }")
+    print("__device__ __forceinline__ p2 p2_sub(p2 a, p2 b) { p2 r; asm(\"sub.rn.f32x2 %0, %1, %2;\" : \"=l\"(r) : \"l\"(a), \"l\"(b)); return r; }")
+    print("__device__ __forceinline__ p2 p2_mul(p2 a, p2 b) { p2 r; asm(\"mul.rn.f32x2 %0, %1, %2;\" : \"=l\"(r) : \"l\"(a), \"l\"(b)); return r; }")
+    print("__device__ __forceinline__ p2 p2_fma(p2 a, p2 b, p2 c) { p2 r; asm(\"fma.rn.f32x2 %0, %1, %2, %3;\" : \"=l\"(r) : \"l\"(a), \"l\"(b), \"l\"(c)); return r; }")
+    print("#endif")
     print("template <int R> struct Radix;")
     print("template <> struct Radix<1> { static CVB_HD void fwd(float (&)[1], float (&)[1]) {} };")
     print()
