@@ -609,7 +609,7 @@ __device__ void body(const Params& P, unsigned char* smem_raw) {
                 const int oy = y - F.p, ox = pos - F.p;
                 if (oy >= 0 && oy < F.H && ox >= 0 && ox < F.W) {
                   float va = v[i].x, vb = -v[i].y;
-                  if (F.fuse_gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
+                  if (F.fuse_gelu) gelu_pair(va, vb);
                   const size_t off = (size_t)oy * F.W + ox;
                   st_io<IO>((IO*)F.out + (size_t)id.pa * in_plane, off, va);
                   if (id.pb >= 0) st_io<IO>((IO*)F.out + (size_t)id.pb * in_plane, off, vb);
@@ -672,7 +672,7 @@ __device__ void epilogue_body(const Params& P) {
             accb = fmaf(kv, rv.y, accb);
           }
         }
-        if (F.fuse_gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+        if (F.fuse_gelu) gelu_pair(acca, accb);
         const size_t off = (size_t)(my * s + da) * oW + (size_t)(mx * s + db);
         st_io<IO>((IO*)F.out + (size_t)pa * out_plane, off, acca);
         if (pb >= 0) st_io<IO>((IO*)F.out + (size_t)pb * out_plane, off, accb);

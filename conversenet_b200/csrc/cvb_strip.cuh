@@ -438,7 +438,7 @@ CVB_HD void tile_store_crop(int tid, int nthr, const float2* tile, int tp, int n
     if (ox < 0 || ox >= P.W) continue;
     const float2 v = tile[(oy + P.p) * tp + col];
     float va = v.x, vb = v.y;
-    if (io.gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
+    if (io.gelu) gelu_pair(va, vb);
     const size_t off = (size_t)oy * P.W + ox;
     st_io<IO>(io.oa, off, va);
     if (io.ob) st_io<IO>(io.ob, off, vb);
@@ -479,7 +479,7 @@ CVB_HD void tile_epilogue(int tid, int nthr, const float2* tile, int tp, int nc,
             accb = fmaf(kv, rv.y, accb);
           }
         }
-        if (io.gelu) { acca = gelu_erf(acca); accb = gelu_erf(accb); }
+        if (io.gelu) gelu_pair(acca, accb);
         const size_t off = (size_t)(my * s + da) * oW + (size_t)(mx * s + db);
         st_io<IO>(io.oa, off, acca);
         if (io.ob) st_io<IO>(io.ob, off, accb);

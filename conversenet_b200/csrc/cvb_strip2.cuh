@@ -328,7 +328,7 @@ CVB_HD void tile_store_crop2(int tid, int nthr, const float2* tile, int tp, int 
   for (int oy = lm.row0; oy < P.H; oy += lm.step) {
     const float2 v = tile[(oy + P.p) * tp + lm.lc];
     float va = v.x, vb = v.y;
-    if (io.gelu) { va = gelu_erf(va); vb = gelu_erf(vb); }
+    if (io.gelu) gelu_pair(va, vb);
     const size_t off = (size_t)oy * P.W + ox;
     st_io<IO>(io.oa, off, va);
     if (io.ob) st_io<IO>(io.ob, off, vb);

@@ -253,9 +253,15 @@ __global__ void __launch_bounds__(T3Threads<MODE>::value, 1) tc3_pw_kernel(const
         float a32[32];
         tc::tmem_ld32(tmem + ((uint32_t)(cw * 32) << 16) + (uint32_t)(acc * N + cbase + c0), a32);
         if (MODE == 0) {
+#ifdef __CUDA_ARCH__   // (the packed helpers exist in the device pass only)
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            st_io<IO>(ob, (size_t)(c0 + j) * P.HW, gelu_erf(a32[j] + bias[cbase + c0 + j]));
+          for (int j = 0; j < 32; j += 2) {
+            const float2 bj = *(const float2*)(bias + cbase + c0 + j);
+            const float2 g = gelu_erf2(a32[j] + bj.x, a32[j + 1] + bj.y);
+            st_io<IO>(ob, (size_t)(c0 + j) * P.HW, g.x);
+            st_io<IO>(ob, (size_t)(c0 + j + 1) * P.HW, g.y);
+          }
+#endif
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
