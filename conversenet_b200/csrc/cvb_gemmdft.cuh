@@ -66,10 +66,9 @@ struct Geo {
   static constexpr int TMEM_COLS = 2 * NB <= 32 ? 32 : 2 * NB <= 64 ? 64 : 2 * NB <= 128 ? 128 : 2 * NB <= 256 ? 256 : 512;
 };
 
-// ring slots of 32 columns (xr hi, xr lo, xi hi, xi lo: 8 each) behind the two accumulators
-template <int R0> CVB_HD constexpr int tmem_a_slots() {
-  return (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 < 4 ? (Geo<R0>::TMEM_COLS - 2 * Geo<R0>::NB) / 32 : 4;
-}
+// Ring slots of 32 columns (xr hi, xr lo, xi hi, xi lo: 8 each) behind the two accumulators.  Two: measured
+// against three, four and seven slots, two were as fast (268) or faster (512, 516: 2 - 4 %).
+template <int R0> CVB_HD constexpr int tmem_a_slots() { return 2; }
 
 // Shared memory beside the constant operand holds the first chunks of a block's NEXT tile, fetched ahead
 // (cp.async, 8 KB per chunk: 128 rows x 8 K x float2) while the current tile is read back: as many chunks
@@ -345,7 +344,7 @@ __device__ __forceinline__ void bar_sync(int id) {
 // issues the MMAs: it waits on the
 // named barrier of a ring slot for the 256 arrivals of the chunk staged there, issues the chunk's six
 // MMAs and commits them to the slot's mbarrier, which is what a staging thread waits for before it
-// reuses the slot -- so staging never waits for the issue, only for the tensor cores three chunks back.
+// reuses the slot -- so staging never waits for the issue, only for the tensor cores one slot round back.
 // Before the first chunk of a tile the issuing warp waits on one more named barrier until every thread
 // has read the previous tile's accumulators, so a warp that has finished its read-back stages the next
 // tile while the others still read.  After a time-out (ok == false) a thread stops waiting and working
